@@ -69,12 +69,12 @@ class CacheManager:
                 for index, group in enumerate(groups):
                     # (layers whose keys or values use other columns of a row do not share pages: the unused columns
                     # of a page must stay zero for whoever gets it next)
-                    if (group.kv_heads, group.head_dim, group.window, group.key_dim, group.value_dim) == (
-                            need.kv_heads, need.head_dim, need.window, need.key_dim, need.value_dim):
+                    if (group.kv_heads, group.head_dim, group.window, group.key_dim, group.value_dim, group.keep_first) == (
+                            need.kv_heads, need.head_dim, need.window, need.key_dim, need.value_dim, need.keep_first):
                         break
                 else:
                     groups.append(GroupSpec(need.kv_heads, need.head_dim, need.window, key_dim=need.key_dim,
-                                            value_dim=need.value_dim))
+                                            value_dim=need.value_dim, keep_first=need.keep_first))
                     index = len(groups) - 1
                 self._layer_place[layer] = ("kv", index, len(groups[index].layers))
                 groups[index].layers.append(layer)

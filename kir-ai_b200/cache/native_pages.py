@@ -37,6 +37,7 @@ def _library() -> ctypes.CDLL:
             "kirai_pages_table": [ctypes.c_long, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int],
             "kirai_pages_fill_tables": [ctypes.POINTER(ctypes.c_long), ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int],
             "kirai_pages_stat": [ctypes.c_int, ctypes.c_int], "kirai_pages_check": [],
+            "kirai_pages_set_keep_first": [ctypes.c_int, ctypes.c_long],
         }.items():
             fn = getattr(lib, name)
             fn.restype = ctypes.c_int
@@ -135,6 +136,9 @@ class NativePageTables:
         self._handle = self._lib.kirai_pages_create(len(groups), windows, page_size, counts, num_slots)
         if not self._handle:
             raise CacheError("the native page tables could not be created")
+        for index, group in enumerate(groups):
+            if getattr(group, "keep_first", 0):
+                self._lib.kirai_pages_set_keep_first(self._handle, index, int(group.keep_first))
         self.pools = [_PoolView(self, g) for g in range(len(groups))]
         self.slots = _SlotsView(self)
         self.live: Dict[object, NativeRequest] = {}

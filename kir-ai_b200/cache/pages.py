@@ -111,6 +111,7 @@ class GroupSpec:
     layers: List[int] = field(default_factory=list)  # cache-layer ids in this group
     key_dim: Optional[int] = None    # columns of a row that keys use (None: all)
     value_dim: Optional[int] = None  # columns of a row that values use (None: all)
+    keep_first: int = 0  # a window never gives back the pages of a request's first so many tokens
 
 
 @dataclass(eq=False)
@@ -186,7 +187,7 @@ class PageTables:
     def commit(self, request: RequestPages, new_tokens: int) -> None:
         """Records that ``new_tokens`` tokens were written, and gives back the pages
         of windowed groups that no later token can see: page p is free once
-        ``(p + 1) * page_size <= length - window + 1``."""
+        ``(p + 1) * page_size <= length - window + 1``, unless it holds one of the group's ``keep_first`` tokens."""
         if request.closed:
             raise CacheError(f"request {request.request_id!r} is closed")
         new_length = request.length + new_tokens
@@ -203,10 +204,11 @@ class PageTables:
             if first_visible <= 0:
                 continue
             dead = min(first_visible // self.page_size, len(table))
-            stale = [table[p] for p in range(dead) if table[p] != NO_PAGE]
+            kept = -(-group.keep_first // self.page_size)
+            stale = [table[p] for p in range(kept, dead) if table[p] != NO_PAGE]
             if stale:
                 pool.release(stale)
-                for p in range(dead):
+                for p in range(kept, dead):
                     table[p] = NO_PAGE
                 request.version += 1
 

@@ -73,7 +73,7 @@ struct WarpState {
 template <int D, int BN, int QROWS, bool Q_IN_REGS>
 __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, int q_row0, const uint32_t (*q_regs)[4], uint32_t k_smem,
                                             uint32_t v_smem, int j0, const int (&lo)[2], const int (&hi)[2],
-                                            const ScoreForm& form, int lane) {
+                                            const ScoreForm& form, int lane, int keep = 0) {
     float s[BN / 8][4];
 #pragma unroll
     for (int n = 0; n < BN / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
@@ -112,15 +112,31 @@ __device__ __forceinline__ void warp_attend(WarpState<D>& st, uint32_t q_smem, i
     // mask, running maximum
     const int col0 = j0 + 2 * (lane & 3);
     float m_new[2] = {st.m[0], st.m[1]};
+    if (keep > j0) {
+        // a tile that holds kept first keys of the sequence: those stay visible below the window (a branch of its own,
+        // which launches without kept keys never take)
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n) {
+        for (int n = 0; n < BN / 8; ++n) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int r = e >> 1;
-            const int j = col0 + n * 8 + (e & 1);
-            const bool visible = j >= lo[r] && j <= hi[r];
-            s[n][e] = visible ? s[n][e] * scale_log2 : -INFINITY;
-            m_new[r] = fmaxf(m_new[r], s[n][e]);
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const int j = col0 + n * 8 + (e & 1);
+                const bool visible = (j >= lo[r] || j < keep) && j <= hi[r];
+                s[n][e] = visible ? s[n][e] * scale_log2 : -INFINITY;
+                m_new[r] = fmaxf(m_new[r], s[n][e]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = e >> 1;
+                const int j = col0 + n * 8 + (e & 1);
+                const bool visible = j >= lo[r] && j <= hi[r];
+                s[n][e] = visible ? s[n][e] * scale_log2 : -INFINITY;
+                m_new[r] = fmaxf(m_new[r], s[n][e]);
+            }
         }
     }
 #pragma unroll
@@ -321,9 +337,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
     const int last_row = min(rows_total, row0 + PF_ROWS) - 1;
     const int pos_first = start_pos + row0 / group;
     const int pos_last = start_pos + last_row / group;
+    const int keep = mask_keep(window);
+    window = mask_window(window);
     const int key_lo = first_visible_key(pos_first, window);
-    const int first_tile = key_lo / PF_BN, last_tile = pos_last / PF_BN;
-    const int num_tiles = last_tile - first_tile + 1;
+    const TileRuns runs = tile_runs(key_lo, keep, PF_BN);
+    const int first_tile = runs.first, last_tile = pos_last / PF_BN;
+    const int num_tiles = runs.kept + last_tile - first_tile + 1;
     bool ok = true;
 
     if (warp == PF_WARPS) {
@@ -333,7 +352,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
         const int* table = block_table + (long)req * table_width;
         if (D <= 128) {
             int* table_s = reinterpret_cast<int*>(smem);
-            const int first_page = (first_tile * PF_BN) / page_size;
+            const int first_page = runs.kept ? 0 : (first_tile * PF_BN) / page_size;
             const int last_page = min(table_width - 1, pos_last / page_size);
             if (last_page - first_page < Smem::q_bytes / 4 && sm100::mbar_wait(sm100::smem_addr(q_free), 0)) {
                 for (int i = first_page + lane; i <= last_page; i += 32) table_s[i - first_page] = table[i];
@@ -349,7 +368,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
             }
             const uint32_t k_dst = ring + slot * 2 * Smem::tile_bytes;
             fill_kv_slot<PF_BN, PANELS>(&kv_map, sm100::smem_addr(&full_bar[slot]), k_dst, k_dst + Smem::tile_bytes,
-                                        first_tile + it, pos_last, table, table_width, num_pages, kv_heads, kv_head,
+                                        runs.tile(it), pos_last, table, table_width, num_pages, kv_heads, kv_head,
                                         page_size, box_rows, lane);
         }
         if (!ok && lane == 0) atomicExch(error_flag, 4);
@@ -388,17 +407,17 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16*
     const int warp_key_lo = warp_first_row < rows_total ? first_visible_key(start_pos + warp_first_row / group, window) : 0;
     for (int it = 0; it < num_tiles; ++it) {
         const int slot = it % PF_STAGES;
-        const int t = first_tile + it;
+        const int t = runs.tile(it);
         if (!sm100::mbar_wait(sm100::smem_addr(&full_bar[slot]), (uint32_t)(it / PF_STAGES) & 1u)) {
             ok = false;
             break;
         }
         // a warp whose rows all lie before this tile, or whose windows all start after it, adds nothing
-        const bool warp_active = warp_pos_last >= t * PF_BN && warp_key_lo < (t + 1) * PF_BN;
+        const bool warp_active = warp_pos_last >= t * PF_BN && (warp_key_lo < (t + 1) * PF_BN || keep > t * PF_BN);
         if (warp_active) {
             const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
             warp_attend<D, PF_BN, PF_ROWS, Q_IN_REGS>(st, q_smem, warp * 16, q_regs, k_s, k_s + Smem::tile_bytes, t * PF_BN, lo, hi,
-                                                     form, lane);
+                                                     form, lane, keep);
         }
         __syncwarp();
         if (lane == 0) sm100::mbar_arrive(sm100::smem_addr(&empty_bar[slot]));
@@ -449,7 +468,8 @@ struct HeadState {
 // q_b[kk] are the B-operand fragments of Q^T for dims 16 kk .. 16 kk + 15.
 template <int D, int BN>
 __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32_t (*q_b)[2], uint32_t k_smem,
-                                                  uint32_t v_smem, int j0, int lo, int hi, const ScoreForm& form, int lane) {
+                                                  uint32_t v_smem, int j0, int lo, int hi, const ScoreForm& form, int lane,
+                                                  int keep = 0) {
     constexpr int MT = BN / 16;
     float s[MT][4];
 #pragma unroll
@@ -465,6 +485,7 @@ __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32
     // mask by key position (rows g and g + 8 of each m-tile), running maximum per head
     const int g = lane >> 2;
     const bool interior = j0 >= lo && j0 + BN - 1 <= hi;
+    const bool has_kept = keep > j0;  // the tile holds kept first keys of the sequence, visible below the window
     // (a soft cap behind a branch of its own, as in warp_attend)
     if (form.cap_log2 != 0.0f) {
 #pragma unroll
@@ -480,7 +501,7 @@ __device__ __forceinline__ void warp_attend_heads(HeadState<D>& st, const uint32
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int j = j0 + mt * 16 + g + (e >> 1) * 8;
-            const bool visible = interior || (j >= lo && j <= hi);
+            const bool visible = interior || ((j >= lo || (has_kept && j < keep)) && j <= hi);
             s[mt][e] = visible ? s[mt][e] * scale_log2 : -INFINITY;
             m_new[e & 1] = fmaxf(m_new[e & 1], s[mt][e]);
         }
@@ -714,11 +735,13 @@ __device__ __forceinline__ void append_new_token(const DecodeArgs& args, const f
 // dst_partial is null, normalised to `out`.  k_base: how many tiles this warp has put through its ring before (the
 // barriers' phases go on from there); the number for the next call is returned.  With `first` the call is the
 // CTA's first work: the tiles that earlier steps filled are requested before griddepcontrol.wait, the rest after.
+// t_begin and t_end count the tiles that the query walks (`runs`: a window that keeps the sequence's first `keep` keys
+// walks those keys' tiles and then the window's; without kept keys walked tile v is key tile runs.first + v).
 template <int D, bool HEADS>
 __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, const DecodeArgs& args, uint8_t* smem, int req,
                                                    int kv_head, int pos, int key_lo, int last_tile, int t_begin, int t_end,
                                                    int k_base, bool first, bf16* __restrict__ out,
-                                                   float* __restrict__ dst_partial, long partial_stride) {
+                                                   float* __restrict__ dst_partial, long partial_stride, TileRuns runs, int keep) {
     using Smem = DecodeSmem<D>;
     constexpr int BN = Smem::BN;
     constexpr int DC_WARPS = Smem::DC_WARPS;
@@ -761,8 +784,8 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
             for (int i = tid; i < table_width; i += THREADS) table_s[i] = table[i];
             table = table_s;
         } else {
-            const int first_page = (t_begin * BN) / page_size;
-            const int last_page = min(table_width - 1, (min(t_end, last_tile + 1) * BN - 1) / page_size);
+            const int first_page = (runs.tile(t_begin) * BN) / page_size;
+            const int last_page = min(table_width - 1, ((min(runs.tile(max(t_end - 1, t_begin)), last_tile) + 1) * BN - 1) / page_size);
             if (last_page - first_page < Smem::table_entries) {
                 for (int i = first_page + tid; i <= last_page; i += THREADS) table_s[i - first_page] = table[i];
                 table = table_s - first_page;
@@ -798,8 +821,8 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
     uint32_t early = 0u;
     if (first) {
         for (int k = 0; k < DC_STAGES && k < my_count; ++k) {
-            if (my_first + k * DC_WARPS < last_tile) {
-                issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
+            if (runs.tile(my_first + k * DC_WARPS) < last_tile) {
+                issue(runs.tile(my_first + k * DC_WARPS), (k_base + k) % DC_STAGES);
                 early |= 1u << k;
             }
         }
@@ -856,7 +879,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
         HeadState<D> st;
         st.init();
         for (int k = 0; k < DC_STAGES && k < my_count; ++k)
-            if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
+            if (!((early >> k) & 1u)) issue(runs.tile(my_first + k * DC_WARPS), (k_base + k) % DC_STAGES);
         for (int k = 0; k < my_count; ++k) {
             const int slot = (k_base + k) % DC_STAGES;
             if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)((k_base + k) / DC_STAGES) & 1u)) {
@@ -864,11 +887,12 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
                 break;
             }
             const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
-            if (args.fuse && my_first + k * DC_WARPS == last_tile)
+            const int t = runs.tile(my_first + k * DC_WARPS);
+            if (args.fuse && t == last_tile)
                 append_new_token<D, BN>(args, rope_s, k_weight_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
-            warp_attend_heads<D, BN>(st, q_b, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, key_lo, pos, form, lane);
+            warp_attend_heads<D, BN>(st, q_b, k_s, k_s + Smem::tile_bytes, t * BN, key_lo, pos, form, lane, keep);
             __syncwarp();
-            if (k + DC_STAGES < my_count) issue(my_first + (k + DC_STAGES) * DC_WARPS, slot);
+            if (k + DC_STAGES < my_count) issue(runs.tile(my_first + (k + DC_STAGES) * DC_WARPS), slot);
         }
         if (!ok && lane == 0) atomicExch(args.error_flag, 4);
         __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
@@ -910,7 +934,7 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
     WarpState<D> st;
     st.init();
     for (int k = 0; k < DC_STAGES && k < my_count; ++k)
-            if (!((early >> k) & 1u)) issue(my_first + k * DC_WARPS, (k_base + k) % DC_STAGES);
+            if (!((early >> k) & 1u)) issue(runs.tile(my_first + k * DC_WARPS), (k_base + k) % DC_STAGES);
     for (int k = 0; k < my_count; ++k) {
         const int slot = (k_base + k) % DC_STAGES;
         if (!sm100::mbar_wait(sm100::smem_addr(&bars[slot]), (uint32_t)((k_base + k) / DC_STAGES) & 1u)) {
@@ -918,12 +942,12 @@ __device__ __forceinline__ int decode_attend_range(const CUtensorMap& kv_map, co
             break;
         }
         const uint32_t k_s = ring + slot * 2 * Smem::tile_bytes;
-        if (args.fuse && my_first + k * DC_WARPS == last_tile)
+        const int t = runs.tile(my_first + k * DC_WARPS);
+        if (args.fuse && t == last_tile)
             append_new_token<D, BN>(args, rope_s, k_weight_s, table, req, kv_head, pos, k_s, k_s + Smem::tile_bytes, lane);
-        warp_attend<D, BN, 16, Q_IN_REGS>(st, q_smem, 0, q_regs, k_s, k_s + Smem::tile_bytes, (my_first + k * DC_WARPS) * BN, lo, hi,
-                                          form, lane);
+        warp_attend<D, BN, 16, Q_IN_REGS>(st, q_smem, 0, q_regs, k_s, k_s + Smem::tile_bytes, t * BN, lo, hi, form, lane, keep);
         __syncwarp();
-        if (k + DC_STAGES < my_count) issue(my_first + (k + DC_STAGES) * DC_WARPS, slot);
+        if (k + DC_STAGES < my_count) issue(runs.tile(my_first + (k + DC_STAGES) * DC_WARPS), slot);
     }
     if (!ok && lane == 0) atomicExch(args.error_flag, 4);
     __syncthreads();  // every warp is done with its ring: it becomes the merge buffer
@@ -1017,12 +1041,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
     const int split = blockIdx.x, kv_head = blockIdx.y, req = blockIdx.z;
     const int group = args.q_heads / args.kv_heads;
     const int pos = context_len[req] - 1;
-    const int key_lo = first_visible_key(pos, args.window);
-    const int first_tile = key_lo / BN, last_tile = pos / BN;
-    const int tiles = last_tile - first_tile + 1;
+    const int keep = mask_keep(args.window);
+    const int key_lo = first_visible_key(pos, mask_window(args.window));
+    const TileRuns runs = tile_runs(key_lo, keep, BN);
+    const int last_tile = pos / BN;
+    const int tiles = runs.kept + last_tile - runs.first + 1;  // walked tiles, see decode_attend_range
     const int per_split = (tiles + num_splits - 1) / num_splits;
-    const int t_begin = first_tile + split * per_split;
-    const int t_end = min(last_tile + 1, t_begin + per_split);
+    const int t_begin = split * per_split;
+    const int t_end = min(tiles, t_begin + per_split);
     if (threadIdx.x == 0) sm100::tma_prefetch_descriptor(&kv_map);
     decode_init_barriers<D>(smem);
     if (PAIR) {
@@ -1037,7 +1063,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
             dst = reinterpret_cast<float*>((uintptr_t)mapped);
         }
         decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
-                                      dst, (long)stride);
+                                      dst, (long)stride, runs, keep);
         // the rows are in place in the first CTA (release), which may read them after the meeting (acquire)
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         if (split == 0) {
@@ -1062,7 +1088,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a
     float* dst_partial = num_splits == 1 ? nullptr
         : partial + (((size_t)req * args.q_heads + kv_head * group) * num_splits + split) * (args.head_dim + 2);
     decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile, t_begin, t_end, 0, true, out,
-                                  dst_partial, (long)num_splits * (args.head_dim + 2));
+                                  dst_partial, (long)num_splits * (args.head_dim + 2), runs, keep);
     decode_stamp(args, 4);
 }
 
@@ -1078,8 +1104,8 @@ __device__ __forceinline__ void decode_tile_prefix(const int* __restrict__ conte
         const int pos = context_len[r] - 1;
         int tiles = 0;
         if (pos >= 0) {
-            const int key_lo = first_visible_key(pos, window);
-            tiles = pos / tile_keys - key_lo / tile_keys + 1;
+            const TileRuns runs = tile_runs(first_visible_key(pos, mask_window(window)), mask_keep(window), tile_keys);
+            tiles = runs.kept + pos / tile_keys - runs.first + 1;
         }
         prefix[r + 1] = tiles;
     }
@@ -1142,8 +1168,10 @@ attention_decode_balanced_kernel(const __grid_constant__ CUtensorMap kv_map, Dec
         const int tiles = prefix[req + 1] - prefix[req];
         if (tiles == 0) continue;
         const int pos = context_len[req] - 1;
-        const int key_lo = first_visible_key(pos, window);
-        const int first_tile = key_lo / BN, last_tile = pos / BN;
+        const int keep = mask_keep(window);
+        const int key_lo = first_visible_key(pos, mask_window(window));
+        const TileRuns runs = tile_runs(key_lo, keep, BN);
+        const int last_tile = pos / BN;
         const int head_first = begin > pair_begin ? (int)((begin - pair_begin) / tiles) : 0;
         for (int kv_head = head_first; kv_head < kv_heads; ++kv_head) {
             const long start = pair_begin + (long)kv_head * tiles;
@@ -1154,8 +1182,8 @@ attention_decode_balanced_kernel(const __grid_constant__ CUtensorMap kv_map, Dec
                 : partial + ((size_t)blockIdx.x * 2 + (from == begin ? 0 : 1)) * 16 * (args.head_dim + 2);
             if (!first) __syncthreads();  // the merge buffer of the range before lies over the ring
             k_base = decode_attend_range<D, HEADS>(kv_map, args, smem, req, kv_head, pos, key_lo, last_tile,
-                                                   first_tile + (int)(from - start), first_tile + (int)(to - start),
-                                                   k_base, first, out, dst_partial, (long)(args.head_dim + 2));
+                                                   (int)(from - start), (int)(to - start), k_base, first, out, dst_partial,
+                                                   (long)(args.head_dim + 2), runs, keep);
             first = false;
         }
     }

@@ -33,7 +33,9 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ cach
     const int kv_head = head / (q_heads / kv_heads);
     const int pos = positions[token];
     const int* table = block_table + (long)request_of_token[token] * table_width;
-    const int lo = first_visible_key(pos, window);
+    const int keep = mask_keep(window);
+    const int lo = first_visible_key(pos, mask_window(window));
+    const int kept = keep < lo ? keep : lo;  // kept first keys that the window no longer covers
 
     const T* q_row = q + (size_t)token * q_row_stride + (size_t)head * head_dim;
     for (int i = threadIdx.x; i < head_dim; i += blockDim.x) q_s[i] = to_f32<T>(q_row[i]);
@@ -44,7 +46,8 @@ paged_attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ cach
 #pragma unroll
     for (int n = 0; n < ATT_MAX_PER_LANE; ++n) o[n] = 0.0f;
 
-    for (int j = lo + warp; j <= pos; j += ATT_WARPS) {
+    for (int at = warp; at < kept + pos - lo + 1; at += ATT_WARPS) {
+        const int j = at < kept ? at : lo + at - kept;
         const int logical = j / page_size;
         const int page = logical < table_width ? table[logical] : -1;
         if (page < 0 || page >= num_pages) {

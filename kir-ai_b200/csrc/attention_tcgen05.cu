@@ -175,9 +175,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
     const int last_row = min(rows_total, row0 + TA_ROWS) - 1;
     const int pos_first = start_pos + row0 / group;
     const int pos_last = start_pos + last_row / group;
+    // a window may keep the sequence's first keys: their tiles are walked first, then the window's (see tile_runs)
+    const int keep = mask_keep(window);
+    window = mask_window(window);
     const int key_lo = first_visible_key(pos_first, window);
-    const int first_tile = key_lo / TA_BN, last_tile = pos_last / TA_BN;
-    const int num_tiles = last_tile - first_tile + 1;
+    const TileRuns runs = tile_runs(key_lo, keep, TA_BN);
+    const int first_tile = runs.first, last_tile = pos_last / TA_BN;
+    const int num_tiles = runs.kept + last_tile - first_tile + 1;
 
     if (tid == 0) {
         tma_prefetch_descriptor(&kv_map);
@@ -214,7 +218,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         }
         // the block table of the keys this CTA reads
         const int* table_g = block_table + (long)req * table_width;
-        const int first_page = (first_tile * TA_BN) / page_size;
+        const int first_page = runs.kept ? 0 : (first_tile * TA_BN) / page_size;
         const int last_page = min(table_width - 1, pos_last / page_size);
         if (last_page - first_page < Smem::table_entries)
             for (int i = first_page + tid; i <= last_page; i += TA_THREADS) table_s[i - first_page] = table_g[i];
@@ -233,7 +237,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         const int which = warp == 0 ? 0 : 1;
         const int* table = block_table + (long)req * table_width;
         {
-            const int first_page = (first_tile * TA_BN) / page_size;
+            const int first_page = runs.kept ? 0 : (first_tile * TA_BN) / page_size;
             const int last_page = min(table_width - 1, pos_last / page_size);
             if (last_page - first_page < Smem::table_entries) table = table_s - first_page;
         }
@@ -313,7 +317,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         uint64_t* full = which == 0 ? k_full : v_full;
         uint64_t* empty = which == 0 ? k_empty : v_empty;
         for (int it = 0; it < num_tiles; ++it) {
-            const TilePlan plan = plan_tile(first_tile + it);
+            const TilePlan plan = plan_tile(runs.tile(it));
             const int slot = it % TA_STAGES;
             if (it >= TA_STAGES && !mbar_wait_hot(smem_addr(&empty[slot]), (uint32_t)(it / TA_STAGES - 1) & 1u)) { ok = false; break; }
             fill(plan, which, smem_addr(&full[slot]), ring + (which * TA_STAGES + slot) * Smem::tile_bytes);
@@ -375,7 +379,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
         float m_used = -INFINITY;  // the maximum that the accumulator and the sum are scaled by (log2 domain)
         float l = 0.0f;
         for (int it = 0; it < num_tiles; ++it) {
-            const int j0 = (first_tile + it) * TA_BN;
+            const int j0 = runs.tile(it) * TA_BN;
             // S of this tile is complete in buffer it & 1
             if (!mbar_wait_hot(smem_addr(&s_ready[it & 1]), (uint32_t)(it >> 1) & 1u)) { ok = false; break; }
             tc_fence_after();
@@ -406,7 +410,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const bf
 #pragma unroll
                 for (int i = 0; i < TA_BN; ++i) {
                     const int j = j0 + i;
-                    if (!(j >= lo && j <= pos)) s[i] = __float_as_uint(-INFINITY);
+                    if (!((j >= lo || j < keep) && j <= pos)) s[i] = __float_as_uint(-INFINITY);
                 }
             }
             // the row's maximum (four running maxima, so that the chain of dependent compares is short)

@@ -25,6 +25,7 @@ SOURCES = [
     "elementwise.cu",
     "layer_forms.cu",
     "mixer_forms.cu",
+    "state_forms.cu",
     "experts.cu",
     "gemm_simt.cu",
     "attention_plain.cu",

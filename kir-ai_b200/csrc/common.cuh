@@ -83,6 +83,32 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // `window` > 0: the last `window` keys up to the query's own position; `window` < 0: the keys of the query's own
 // chunk of -window positions (chunks counted from position 0 of the sequence); 0: every key up to its own position.
 // The first visible key never decreases with the position.
+// A window may also keep a sequence's first `keep` keys visible to every later position, at their true positions:
+// position i sees j <= i when i - j < window or j < keep.  Such a mask travels in the same integer as
+// window + (keep << MASK_KEEP_SHIFT) (window below 2^20, keep below 2^11); mask_keep and mask_window take it apart, and
+// kernels walk the key tiles [0, ceil(keep / tile)) and then those from the window's first tile on (the two runs
+// joined when they meet), masking key j when first_visible_key(pos, window) > j >= keep.
+#define MASK_KEEP_SHIFT 20
+__host__ __device__ __forceinline__ int mask_keep(int code) { return code > 0 ? code >> MASK_KEEP_SHIFT : 0; }
+__host__ __device__ __forceinline__ int mask_window(int code) { return code > 0 ? code & ((1 << MASK_KEEP_SHIFT) - 1) : code; }
+
+// The key tiles a query range walks under such a mask: `kept` tiles from tile 0, then tiles from `first` on.
+// Iteration `it` reads tile it < kept ? it : first + it - kept.
+struct TileRuns {
+    int kept, first;
+    __host__ __device__ __forceinline__ int tile(int it) const { return it < kept ? it : first + it - kept; }
+};
+__host__ __device__ __forceinline__ TileRuns tile_runs(int key_lo, int keep, int tile_keys) {
+    TileRuns runs;
+    runs.first = key_lo / tile_keys;
+    runs.kept = keep > 0 ? (keep + tile_keys - 1) / tile_keys : 0;
+    if (runs.kept >= runs.first) {  // the runs meet: one run from tile 0
+        runs.kept = 0;
+        runs.first = keep > 0 ? 0 : runs.first;
+    }
+    return runs;
+}
+
 __host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
     if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
     if (window < 0) return pos - pos % (-window);

@@ -2,7 +2,8 @@
 //
 //   router_gates   logits z = W_router x in 32-bit (spread over blocks by expert; the block of a token that finishes last goes on);
 //                  the `top` largest are chosen (the lower index wins a tie) and the
-//                  token's weights are the softmax over the chosen logits alone.  The result is the dense matrix
+//                  token's weights are the softmax over the chosen logits alone (or, with `over_all`, the chosen
+//                  experts' shares of the softmax over ALL logits, which then do not sum to one).  The result is the dense matrix
 //                  gates [T, experts], zero where an expert was not chosen, plus the chosen ids and weights.
 //   relu2_gate     hidden[t, e * ff + j] = relu(up[t, e * ff + j])^2 * gates[t, e]: with the experts' up matrices
 //                  stacked along the rows and their down matrices side by side along the columns, the product
@@ -27,12 +28,21 @@ __device__ __forceinline__ float4 load4(const bf16* p) {
 // [experts] of logits (read past L1), picks the `top` largest one after the other (the lower index wins a tie) and
 // overwrites the row with the routing weights.  `logits_s` [experts] is this warp's shared scratch.
 __device__ __forceinline__ void choose_experts(float* __restrict__ out, float* logits_s, int* __restrict__ chosen_ids,
-                                               float* __restrict__ chosen_weights, int experts, int top, int lane) {
+                                               float* __restrict__ chosen_weights, int experts, int top, int lane,
+                                               int over_all = 0) {
     for (int i = lane; i < experts; i += 32) logits_s[i] = __ldcg(out + i);
     __syncwarp();
     for (int i = lane; i < experts; i += 32) out[i] = 0.0f;
     __syncwarp();
-    float best_first = 0.0f, denom = 0.0f;
+    float best_first = 0.0f, denom = 0.0f, all_sum = 0.0f;
+    if (over_all) {
+        // the softmax's denominator over every expert, before any logit is struck out
+        float all_max = -INFINITY;
+        for (int i = lane; i < experts; i += 32) all_max = fmaxf(all_max, logits_s[i]);
+        all_max = warp_max(all_max);
+        for (int i = lane; i < experts; i += 32) all_sum += expf(logits_s[i] - all_max);
+        all_sum = warp_sum(all_sum);
+    }
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
@@ -68,6 +78,7 @@ __device__ __forceinline__ void choose_experts(float* __restrict__ out, float* l
         __syncwarp();
     }
     __syncwarp();
+    if (over_all) denom = all_sum;  // (the first chosen logit is the maximum of all)
     const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
     for (int i = lane; i < experts; i += 32) out[i] *= inv;
     if (chosen_weights)
@@ -96,7 +107,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_gates_few_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ router, float* __restrict__ gates,
                         int* __restrict__ chosen_ids, float* __restrict__ chosen_weights, int* __restrict__ arrivals, int hidden,
-                        int experts, int top) {
+                        int experts, int top, int over_all) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float logits_s[];  // [experts]
@@ -129,7 +140,7 @@ router_gates_few_kernel(const T* __restrict__ x, long x_stride, const float* __r
     if (!arrives_last(&arrivals[token], (int)gridDim.y, &is_last)) return;
     if (warp == 0)
         choose_experts(out, logits_s, chosen_ids ? chosen_ids + (size_t)token * top : nullptr,
-                       chosen_weights ? chosen_weights + (size_t)token * top : nullptr, experts, top, lane);
+                       chosen_weights ? chosen_weights + (size_t)token * top : nullptr, experts, top, lane, over_all);
 }
 
 // Many tokens: a block takes ROUTER_TOKENS tokens and ROUTER_WARPS experts, a warp per expert, so that a router row is
@@ -140,7 +151,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_gates_many_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ router, float* __restrict__ gates,
                          int* __restrict__ chosen_ids, float* __restrict__ chosen_weights, int* __restrict__ arrivals, int tokens,
-                         int hidden, int experts, int top) {
+                         int hidden, int experts, int top, int over_all) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float logits_s[];  // [ROUTER_WARPS][experts]
@@ -184,32 +195,32 @@ router_gates_many_kernel(const T* __restrict__ x, long x_stride, const float* __
     for (int t = warp; t < count; t += ROUTER_WARPS) {
         const size_t token = (size_t)(first + t);
         choose_experts(gates + token * experts, logits_s + (size_t)warp * experts, chosen_ids ? chosen_ids + token * top : nullptr,
-                       chosen_weights ? chosen_weights + token * top : nullptr, experts, top, lane);
+                       chosen_weights ? chosen_weights + token * top : nullptr, experts, top, lane, over_all);
     }
 }
 
 template <typename T>
 static int router_gates_launch(const void* x, long x_stride, const float* router, float* gates, int* chosen_ids,
                                float* chosen_weights, int* arrivals, int tokens, int hidden, int experts, int top,
-                               cudaStream_t stream) {
+                               int over_all, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (experts <= 0 || top <= 0 || top > experts || hidden <= 0 || experts > 8192 || !arrivals) return KIRAI_ERR_BAD_SIZE;
     if ((chosen_ids == nullptr) != (chosen_weights == nullptr)) return KIRAI_ERR_BAD_SIZE;
     if (tokens * (long)experts <= 4096 && experts <= 65535) {
         return launch_pdl(router_gates_few_kernel<T>, dim3(tokens, experts), dim3(ROUTER_WARPS * 32), (size_t)experts * sizeof(float),
-                          stream, 1u, (const T*)x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, hidden, experts, top);
+                          stream, 1u, (const T*)x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, hidden, experts, top, over_all);
     }
     const unsigned slices = (unsigned)((experts + ROUTER_WARPS - 1) / ROUTER_WARPS);
     const unsigned groups = (unsigned)((tokens + ROUTER_TOKENS - 1) / ROUTER_TOKENS);
     return launch_pdl(router_gates_many_kernel<T>, dim3(groups, slices), dim3(ROUTER_WARPS * 32),
                       (size_t)ROUTER_WARPS * experts * sizeof(float), stream, 1u, (const T*)x, x_stride, router, gates, chosen_ids,
-                      chosen_weights, arrivals, tokens, hidden, experts, top);
+                      chosen_weights, arrivals, tokens, hidden, experts, top, over_all);
 }
 
 // The choice alone, for logits that a product left in `gates` [tokens, experts]: a warp per token.
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_choose_kernel(float* __restrict__ gates, int* __restrict__ chosen_ids, float* __restrict__ chosen_weights, int tokens,
-                     int experts, int top) {
+                     int experts, int top, int over_all) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float logits_s[];  // [ROUTER_WARPS][experts]
@@ -217,29 +228,29 @@ router_choose_kernel(float* __restrict__ gates, int* __restrict__ chosen_ids, fl
     const size_t token = (size_t)blockIdx.x * ROUTER_WARPS + warp;
     if (token >= (size_t)tokens) return;
     choose_experts(gates + token * experts, logits_s + (size_t)warp * experts, chosen_ids ? chosen_ids + token * top : nullptr,
-                   chosen_weights ? chosen_weights + token * top : nullptr, experts, top, lane);
+                   chosen_weights ? chosen_weights + token * top : nullptr, experts, top, lane, over_all);
 }
 
 // gates [tokens, experts] holds router logits (32-bit) and receives the routing weights; see router_gates.
 KIRAI_EXPORT int kirai_router_choose(float* gates, int* chosen_ids, float* chosen_weights, int tokens, int experts, int top,
-                                     cudaStream_t stream) {
+                                     int over_all, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (experts <= 0 || top <= 0 || top > experts || experts > 8192) return KIRAI_ERR_BAD_SIZE;
     if ((chosen_ids == nullptr) != (chosen_weights == nullptr)) return KIRAI_ERR_BAD_SIZE;
     return launch_pdl(router_choose_kernel, dim3((unsigned)((tokens + ROUTER_WARPS - 1) / ROUTER_WARPS)), dim3(ROUTER_WARPS * 32),
-                      (size_t)ROUTER_WARPS * experts * sizeof(float), stream, 1u, gates, chosen_ids, chosen_weights, tokens, experts, top);
+                      (size_t)ROUTER_WARPS * experts * sizeof(float), stream, 1u, gates, chosen_ids, chosen_weights, tokens, experts, top, over_all);
 }
 
 // arrivals [tokens]: zero before the first launch; every launch leaves it zero.
 KIRAI_EXPORT int kirai_router_gates_f32(const void* x, long x_stride, const float* router, float* gates, int* chosen_ids,
                                         float* chosen_weights, int* arrivals, int tokens, int hidden, int experts, int top,
-                                        cudaStream_t stream) {
-    return router_gates_launch<float>(x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, tokens, hidden, experts, top, stream);
+                                        int over_all, cudaStream_t stream) {
+    return router_gates_launch<float>(x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, tokens, hidden, experts, top, over_all, stream);
 }
 KIRAI_EXPORT int kirai_router_gates_bf16(const void* x, long x_stride, const float* router, float* gates, int* chosen_ids,
                                          float* chosen_weights, int* arrivals, int tokens, int hidden, int experts, int top,
-                                         cudaStream_t stream) {
-    return router_gates_launch<bf16>(x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, tokens, hidden, experts, top, stream);
+                                         int over_all, cudaStream_t stream) {
+    return router_gates_launch<bf16>(x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, tokens, hidden, experts, top, over_all, stream);
 }
 
 // activation: 0 = relu(z)^2

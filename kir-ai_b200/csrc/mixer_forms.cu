@@ -488,12 +488,12 @@ KIRAI_EXPORT int kirai_mingru_bf16(const float* zxg, long row_stride, const floa
 // One block per token.  qkv row (float32): nq heads of dk, then nkv heads of dk, then nkv heads of dv (further
 // columns, as an output gate's, are not touched).  Columns [rot_off, rot_off + rot_dims) of every query and key head
 // are rotated, column i of the first half with column i + rot_dims / 2, by position * inv_freq[i]; query head h is
-// multiplied by q_factor[h].  Queries leave as [nq, dpad] rows with zeros beyond dk; keys and values go to the
+// multiplied by q_factor[h]; cosine and sine are multiplied by rot_amp (1: a plain rotation).  Queries leave as [nq, dpad] rows with zeros beyond dk; keys and values go to the
 // token's row of its page, cache [pages, 2, nkv, page, dpad].
 template <typename T>
 __device__ __forceinline__ void rotate_head_to(const float* __restrict__ src, const float* __restrict__ bias, T* __restrict__ dst,
                                                int width, int rot_off, int rot_dims, const float* __restrict__ inv_freq,
-                                               float pos, float factor, int lane, int lanes) {
+                                               float pos, float factor, int lane, int lanes, float rot_amp = 1.0f) {
     const int half = rot_dims >> 1;
     for (int c = lane; c < width; c += lanes) {
         const int r = c - rot_off;
@@ -503,6 +503,8 @@ __device__ __forceinline__ void rotate_head_to(const float* __restrict__ src, co
             const float v = src[c + half] + (bias ? bias[c + half] : 0.0f);
             float sn, cs;
             sincosf(pos * inv_freq[r], &sn, &cs);
+            sn *= rot_amp;
+            cs *= rot_amp;
             dst[c] = from_f32<T>((u * cs - v * sn) * factor);
             dst[c + half] = from_f32<T>((v * cs + u * sn) * factor);
         } else {
@@ -515,7 +517,7 @@ template <typename T>
 __global__ void qkv_rope_write_kernel(const float* __restrict__ qkv, long qkv_stride, const float* __restrict__ q_bias,
                                       const float* __restrict__ k_bias, const float* __restrict__ v_bias,
                                       const float* __restrict__ q_factor, const float* __restrict__ inv_freq, int rot_off,
-                                      int rot_dims, T* __restrict__ q_out, T* __restrict__ cache,
+                                      int rot_dims, float rot_amp, T* __restrict__ q_out, T* __restrict__ cache,
                                       const int* __restrict__ block_table, const int* __restrict__ request_of_token,
                                       const int* __restrict__ positions, int q_heads, int kv_heads, int dk, int dv, int dpad,
                                       int page_size, int table_width, int num_pages, int* __restrict__ error_flag) {
@@ -542,12 +544,12 @@ __global__ void qkv_rope_write_kernel(const float* __restrict__ qkv, long qkv_st
         if (unit < q_heads) {
             T* dst = q_out + ((size_t)token * q_heads + unit) * dpad;
             rotate_head_to<T>(src + (size_t)unit * dk, q_bias ? q_bias + (size_t)unit * dk : nullptr, dst, dk, rot_off, rot_dims,
-                              inv_freq, pos, q_factor ? q_factor[unit] : 1.0f, lane, 32);
+                              inv_freq, pos, q_factor ? q_factor[unit] : 1.0f, lane, 32, rot_amp);
             for (int c = dk + lane; c < dpad; c += 32) dst[c] = from_f32<T>(0.0f);
         } else if (page_base >= 0 && unit < q_heads + kv_heads) {
             const int head = unit - q_heads;
             rotate_head_to<T>(src + (size_t)q_heads * dk + (size_t)head * dk, k_bias ? k_bias + (size_t)head * dk : nullptr,
-                              cache + page_base + head * head_rows, dk, rot_off, rot_dims, inv_freq, pos, 1.0f, lane, 32);
+                              cache + page_base + head * head_rows, dk, rot_off, rot_dims, inv_freq, pos, 1.0f, lane, 32, rot_amp);
         } else if (page_base >= 0) {
             const int head = unit - q_heads - kv_heads;
             const float* v = src + (size_t)(q_heads + kv_heads) * dk + (size_t)head * dv;
@@ -559,7 +561,7 @@ __global__ void qkv_rope_write_kernel(const float* __restrict__ qkv, long qkv_st
 
 template <typename T>
 static int qkv_rope_write_launch(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias, const float* v_bias,
-                                 const float* q_factor, const float* inv_freq, int rot_off, int rot_dims, void* q_out, void* cache,
+                                 const float* q_factor, const float* inv_freq, int rot_off, int rot_dims, float rot_amp, void* q_out, void* cache,
                                  const int* block_table, const int* request_of_token, const int* positions, int tokens,
                                  int q_heads, int kv_heads, int dk, int dv, int dpad, int page_size, int table_width,
                                  int num_pages, int* error_flag, cudaStream_t stream) {
@@ -570,27 +572,27 @@ static int qkv_rope_write_launch(const float* qkv, long qkv_stride, const float*
     const int units = q_heads + 2 * kv_heads;
     const int threads = units >= 8 ? 256 : 32 * units;
     return launch_pdl(qkv_rope_write_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 1u, qkv, qkv_stride, q_bias, k_bias, v_bias,
-                      q_factor, inv_freq, rot_off, rot_dims, (T*)q_out, (T*)cache, block_table, request_of_token, positions,
+                      q_factor, inv_freq, rot_off, rot_dims, rot_amp, (T*)q_out, (T*)cache, block_table, request_of_token, positions,
                       q_heads, kv_heads, dk, dv, dpad, page_size, table_width, num_pages, error_flag);
 }
 
 KIRAI_EXPORT int kirai_qkv_rope_write_f32(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias,
                                           const float* v_bias, const float* q_factor, const float* inv_freq, int rot_off,
-                                          int rot_dims, void* q_out, void* cache, const int* block_table,
+                                          int rot_dims, float rot_amp, void* q_out, void* cache, const int* block_table,
                                           const int* request_of_token, const int* positions, int tokens, int q_heads,
                                           int kv_heads, int dk, int dv, int dpad, int page_size, int table_width,
                                           int num_pages, int* error_flag, cudaStream_t stream) {
-    return qkv_rope_write_launch<float>(qkv, qkv_stride, q_bias, k_bias, v_bias, q_factor, inv_freq, rot_off, rot_dims, q_out,
+    return qkv_rope_write_launch<float>(qkv, qkv_stride, q_bias, k_bias, v_bias, q_factor, inv_freq, rot_off, rot_dims, rot_amp, q_out,
                                         cache, block_table, request_of_token, positions, tokens, q_heads, kv_heads, dk, dv, dpad,
                                         page_size, table_width, num_pages, error_flag, stream);
 }
 KIRAI_EXPORT int kirai_qkv_rope_write_bf16(const float* qkv, long qkv_stride, const float* q_bias, const float* k_bias,
                                            const float* v_bias, const float* q_factor, const float* inv_freq, int rot_off,
-                                           int rot_dims, void* q_out, void* cache, const int* block_table,
+                                           int rot_dims, float rot_amp, void* q_out, void* cache, const int* block_table,
                                            const int* request_of_token, const int* positions, int tokens, int q_heads,
                                            int kv_heads, int dk, int dv, int dpad, int page_size, int table_width,
                                            int num_pages, int* error_flag, cudaStream_t stream) {
-    return qkv_rope_write_launch<bf16>(qkv, qkv_stride, q_bias, k_bias, v_bias, q_factor, inv_freq, rot_off, rot_dims, q_out,
+    return qkv_rope_write_launch<bf16>(qkv, qkv_stride, q_bias, k_bias, v_bias, q_factor, inv_freq, rot_off, rot_dims, rot_amp, q_out,
                                        cache, block_table, request_of_token, positions, tokens, q_heads, kv_heads, dk, dv, dpad,
                                        page_size, table_width, num_pages, error_flag, stream);
 }

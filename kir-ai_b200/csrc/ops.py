@@ -429,11 +429,11 @@ def qkv_rope_write(qkv: torch.Tensor, q_heads: int, kv_heads: int, key_dim: int,
                    q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor], v_bias: Optional[torch.Tensor],
                    q_factor: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rot_offset: int, rot_dims: int,
                    cache: Optional[torch.Tensor], block_table: torch.Tensor, request_of_token: torch.Tensor,
-                   positions: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+                   positions: torch.Tensor, out_dtype: torch.dtype, rot_amplitude: float = 1.0) -> torch.Tensor:
     """Prepares attention whose projections carry biases and whose heads are rotated in part: ``qkv`` [T, >= nq dk +
     nkv dk + nkv dv] (float32, the stacked product; further columns are left alone; ``kv_heads`` 0 for queries only)
     gets its biases, columns [rot_offset, rot_offset + rot_dims) of every query and key head are rotated (column i of
-    the first half with column i + rot_dims / 2, by position * inv_freq[i]), query head h is multiplied by
+    the first half with column i + rot_dims / 2, by position * inv_freq[i], cosine and sine times ``rot_amplitude``), query head h is multiplied by
     ``q_factor[h]``, keys and values go to the token's page row in ``cache`` [pages, 2, nkv, page, pad_dim], and the
     queries come back as [T, nq, pad_dim] in ``out_dtype`` with zero columns beyond dk."""
     _need_cuda(qkv, q_bias, k_bias, v_bias, q_factor, inv_freq, cache, block_table, request_of_token, positions)
@@ -449,7 +449,7 @@ def qkv_rope_write(qkv: torch.Tensor, q_heads: int, kv_heads: int, key_dim: int,
     tokens = qkv.shape[0]
     q_out = torch.empty((tokens, q_heads, pad_dim), dtype=out_dtype, device=qkv.device)
     _call(f"kirai_qkv_rope_write_{_suffix(out_dtype)}", _ptr(qkv), _l(qkv.stride(0)), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
-          _ptr(q_factor), _ptr(inv_freq if rot_dims else None), _i(rot_offset), _i(rot_dims), _ptr(q_out),
+          _ptr(q_factor), _ptr(inv_freq if rot_dims else None), _i(rot_offset), _i(rot_dims), _f(rot_amplitude), _ptr(q_out),
           _ptr(cache if kv_heads else None), _ptr(block_table), _ptr(request_of_token), _ptr(positions), _i(tokens),
           _i(q_heads), _i(kv_heads), _i(key_dim), _i(value_dim), _i(pad_dim), _i(page_size), _i(block_table.shape[1]),
           _i(num_pages), _ptr(error_flag(qkv.device)), _stream())
@@ -514,6 +514,160 @@ def add_bias_(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
     return x
 
 
+# ------------------------------------------------- Dynamic Tanh, matrix states, convolution
+def add_dyt(resid: torch.Tensor, deltas, factor: float, alpha: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+            out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``resid`` [T, W] (float32, in place) += factor * sum(deltas) (up to two float32 tensors [T, W], or none), then
+    the rows leave as tanh(alpha * x) * weight + bias in ``out_dtype``.  With ``row_index`` (int32 rows) only those rows
+    are produced and the stream is left as it is."""
+    deltas = [d for d in (deltas or []) if d is not None]
+    _need_cuda(resid, alpha, weight, bias, row_index, *deltas)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous() and len(deltas) <= 2
+    width = resid.shape[1]
+    for d in deltas:
+        assert d.dtype == torch.float32 and d.shape == resid.shape and d.is_contiguous()
+    for t, n in ((alpha, 1), (weight, width), (bias, width)):
+        assert t.dtype == torch.float32 and t.numel() == n and t.is_contiguous()
+    rows = resid.shape[0] if row_index is None else row_index.numel()
+    out = torch.empty((rows, width), dtype=out_dtype, device=resid.device)
+    _call(f"kirai_add_dyt_{_suffix(out_dtype)}", _ptr(resid), _ptr(deltas[0] if deltas else None),
+          _ptr(deltas[1] if len(deltas) > 1 else None), _f(factor), _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out),
+          _ptr(row_index), _i(rows), _i(width), _stream())
+    return out
+
+
+def add_scaled_into_residual(resid: torch.Tensor, deltas, factor: float) -> torch.Tensor:
+    """``resid`` (float32, in place) += factor * sum(deltas) (one or two float32 tensors of its shape)."""
+    deltas = [d for d in deltas if d is not None]
+    _need_cuda(resid, *deltas)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and 1 <= len(deltas) <= 2
+    for d in deltas:
+        assert d.dtype == torch.float32 and d.shape == resid.shape and d.is_contiguous()
+    _call("kirai_add_scaled", _ptr(resid), _ptr(deltas[0]), _ptr(deltas[1] if len(deltas) > 1 else None), _f(factor),
+          _l(resid.numel()), _stream())
+    return resid
+
+
+def rms_pair_mean(a: torch.Tensor, b: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor, eps: float) -> torch.Tensor:
+    """(a / rms(a) * weight_a + b / rms(b) * weight_b) / 2 row by row, rms with ``eps`` inside the root; all float32."""
+    _need_cuda(a, b, weight_a, weight_b)
+    assert a.dtype == b.dtype == torch.float32 and a.dim() == 2 and a.shape == b.shape and a.is_contiguous() and b.is_contiguous()
+    for w in (weight_a, weight_b):
+        assert w.dtype == torch.float32 and w.numel() == a.shape[1] and w.is_contiguous()
+    out = torch.empty_like(a)
+    _call("kirai_rms_pair_mean", _ptr(a), _ptr(b), _ptr(weight_a), _ptr(weight_b), _f(eps), _ptr(out), _i(a.shape[0]),
+          _i(a.shape[1]), _stream())
+    return out
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, gate_first: bool,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """``y`` [T, W] (float32; a run of columns of a wider tensor is allowed, as for ``gate``) through a gate and a
+    unit-RMS norm over ``groups`` equal parts of a row (``eps`` inside the root), times ``weight`` [W].
+    ``gate_first``: (y * silu(gate)) is normed; else y is normed and then multiplied by sigmoid(gate)."""
+    _need_cuda(y, gate, weight)
+    assert y.dtype == gate.dtype == torch.float32 and y.dim() == 2 and y.shape == gate.shape and y.stride(1) == gate.stride(1) == 1
+    width = y.shape[1]
+    assert width % groups == 0 and weight.dtype == torch.float32 and weight.numel() == width and weight.is_contiguous()
+    out = torch.empty((y.shape[0], width), dtype=out_dtype, device=y.device)
+    _call(f"kirai_gated_group_norm_{_suffix(out_dtype)}", _ptr(y), _l(y.stride(0)), _ptr(gate), _l(gate.stride(0)), _ptr(weight),
+          _f(eps), _ptr(out), _i(y.shape[0]), _i(groups), _i(width // groups), _i(0 if gate_first else 1), _stream())
+    return out
+
+
+def conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, conv_offset: int,
+              batch) -> torch.Tensor:
+    """Causal convolution per channel with silu over each request's tokens of this step.  ``x`` [T, C] (float32, a
+    run of columns of a wider tensor is allowed); ``taps`` [C, K] (float32), whose last column weighs the token
+    itself; the K - 1 rows before a request's first row of this step come from its slot of ``state`` [slots, L]
+    (float32) at columns [conv_offset, conv_offset + (K - 1) C), which afterwards hold the request's last K - 1 rows."""
+    _need_cuda(x, taps, bias, state)
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
+    channels, width = x.shape[1], taps.shape[1]
+    assert taps.dtype == torch.float32 and taps.shape == (channels, width) and taps.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == channels and bias.is_contiguous())
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    out = torch.empty((x.shape[0], channels), dtype=torch.float32, device=x.device)
+    _call("kirai_conv_silu", _ptr(x), _l(x.stride(0)), _ptr(taps), _ptr(bias), _ptr(state), _l(state.shape[1]), _l(conv_offset),
+          _ptr(batch.request_of_token), _ptr(batch.query_start), _ptr(batch.slots), _ptr(out), _i(x.shape[0]),
+          _i(batch.num_requests), _i(channels), _i(width), _i(state.shape[0]), _stream())
+    return out
+
+
+def ssm_walk(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor,
+             state: torch.Tensor, ssm_offset: int, batch, heads: int, groups: int, state_size: int, head_dim: int) -> torch.Tensor:
+    """The state-space recurrence over each request's tokens of this step.  ``xbc`` [T, H P + 2 G N] (float32): x, B
+    and C; ``dt`` [T, H] (float32, a run of columns of a wider tensor is allowed): step sizes before softplus.  Per
+    head h (group h // (H / G)): dt = softplus(dt + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C +
+    skip x, S [N, P] in the request's slot of ``state`` [slots, L] from column ``ssm_offset``.  Returns y [T, H P]
+    (float32)."""
+    _need_cuda(xbc, dt, dt_bias, a_log, skip, state)
+    inner = heads * head_dim
+    assert xbc.dtype == torch.float32 and xbc.is_contiguous() and xbc.shape[1] == inner + 2 * groups * state_size
+    assert dt.dtype == torch.float32 and dt.shape == (xbc.shape[0], heads) and dt.stride(1) == 1
+    for t in (dt_bias, a_log, skip):
+        assert t.dtype == torch.float32 and t.numel() == heads and t.is_contiguous()
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    y = torch.empty((xbc.shape[0], inner), dtype=torch.float32, device=xbc.device)
+    _call("kirai_ssm_walk", _ptr(xbc), _ptr(dt), _l(dt.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state),
+          _l(state.shape[1]), _l(ssm_offset), _ptr(batch.query_start), _ptr(batch.slots), _ptr(y), _i(batch.num_requests),
+          _i(heads), _i(groups), _i(state_size), _i(head_dim), _i(state.shape[0]), _stream())
+    return y
+
+
+def matrix_memory_walk(rows: torch.Tensor, in_bias: Optional[torch.Tensor], keep_bias: Optional[torch.Tensor], cap: float,
+                       q_scale: float, state: torch.Tensor, batch, heads: int, key_dim: int, value_dim: int) -> torch.Tensor:
+    """The matrix memory with exponential gates over each request's tokens of this step.  ``rows`` (float32; further
+    columns are left alone): q [H d], k [H d], v [H dv], the input gates' [H] and the forget gates' [H]
+    pre-activations.  log_in = cap tanh((. + in_bias) / cap), log_keep = logsigmoid(cap tanh((. + keep_bias) / cap)),
+    m' = max(log_keep + m, log_in), S <- exp(log_keep + m - m') S + exp(log_in - m') k v^T, n likewise with k alone,
+    o = S^T (q q_scale) / (max(|n . q q_scale|, exp(-m')) + 1e-6).  The request's slot of ``state`` [slots, L] holds
+    S [H, d, dv], n [H, d], m [H].  Returns o [T, H dv] (float32)."""
+    _need_cuda(rows, in_bias, keep_bias, state)
+    assert rows.dtype == torch.float32 and rows.dim() == 2 and rows.stride(1) == 1
+    assert rows.shape[1] >= heads * (2 * key_dim + value_dim + 2)
+    for t in (in_bias, keep_bias):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == heads and t.is_contiguous())
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    o = torch.empty((rows.shape[0], heads * value_dim), dtype=torch.float32, device=rows.device)
+    _call("kirai_matrix_memory_walk", _ptr(rows), _l(rows.stride(0)), _ptr(in_bias), _ptr(keep_bias), _f(cap), _f(q_scale),
+          _ptr(state), _l(state.shape[1]), _ptr(batch.query_start), _ptr(batch.slots), _ptr(o), _i(batch.num_requests), _i(heads),
+          _i(key_dim), _i(value_dim), _i(state.shape[0]), _stream())
+    return o
+
+
+def head_gate_(x: torch.Tensor, gate: torch.Tensor, heads: int, used: int, pad_dim: int) -> torch.Tensor:
+    """``x`` [T, heads * pad_dim] (in place): the first ``used`` columns of head h times sigmoid(gate[t, h]); ``gate``
+    [T, heads] (float32; a run of columns of a wider product is allowed)."""
+    _need_cuda(x, gate)
+    assert x.dim() == 2 and x.is_contiguous() and x.shape[1] == heads * pad_dim
+    assert gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == (x.shape[0], heads)
+    _call(f"kirai_head_gate_{_suffix(x.dtype)}", _ptr(x), _ptr(gate), _l(gate.stride(0)), _i(x.shape[0]), _i(heads), _i(used),
+          _i(pad_dim), _stream())
+    return x
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``x`` (float32, in place) <- cap * tanh(x / cap)."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _call("kirai_softcap_rows", _ptr(x), _f(cap), _l(x.numel()), _stream())
+    return x
+
+
+def gated_expert_gate(gate_up: torch.Tensor, gates: torch.Tensor, ff: int, activation: str = "silu") -> torch.Tensor:
+    """Stacked gated experts: ``gate_up`` [T, experts * 2 ff] (per expert ff gate columns, then ff up columns) becomes
+    [T, experts * ff] = act(gate) * up * gates[t, expert] (``gates`` float32 [T, experts], zero where not chosen)."""
+    _need_cuda(gate_up, gates)
+    assert gate_up.dim() == 2 and gate_up.is_contiguous() and gates.dtype == torch.float32 and gates.is_contiguous()
+    experts = gates.shape[1]
+    assert gate_up.shape == (gates.shape[0], experts * 2 * ff)
+    out = torch.empty((gate_up.shape[0], experts * ff), dtype=gate_up.dtype, device=gate_up.device)
+    _call(f"kirai_gated_expert_gate_{_suffix(gate_up.dtype)}", _ptr(gate_up), _ptr(gates), _ptr(out), _i(gate_up.shape[0]),
+          _i(experts), _i(ff), _i(GATED_ACTIVATIONS[activation]), _stream())
+    return out
+
+
 _arrival_counters: dict = {}
 
 
@@ -532,11 +686,12 @@ def _router_arrivals(device: torch.device, tokens: int) -> torch.Tensor:
     return counters
 
 
-def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: bool = False):
+def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: bool = False, over_all: bool = False):
     """Routing weights of every token: logits ``router`` [experts, H] (float32) times ``x`` [T, H] in 32-bit, the ``top``
     largest chosen (the lower index on a tie), softmax over the chosen logits alone.  Returns gates [T, experts]
     (float32, zero where not chosen); with ``want_chosen`` also (ids [T, top] int32, weights [T, top] float32) in the
-    order of choice."""
+    order of choice.  ``over_all``: the weights are the chosen experts' shares of the softmax over ALL logits instead
+    (they then do not sum to one)."""
     _need_cuda(x, router)
     assert x.dim() == 2 and x.stride(1) == 1 and router.dtype == torch.float32 and router.is_contiguous()
     assert router.shape[1] == x.shape[1] and 0 < top <= router.shape[0]
@@ -545,11 +700,11 @@ def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: b
     ids = torch.empty((tokens, top), dtype=torch.int32, device=x.device) if want_chosen else None
     weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device) if want_chosen else None
     _call(f"kirai_router_gates_{_suffix(x.dtype)}", _ptr(x), _l(x.stride(0)), _ptr(router), _ptr(gates), _ptr(ids), _ptr(weights),
-          _ptr(_router_arrivals(x.device, tokens)), _i(tokens), _i(x.shape[1]), _i(experts), _i(top), _stream())
+          _ptr(_router_arrivals(x.device, tokens)), _i(tokens), _i(x.shape[1]), _i(experts), _i(top), _i(int(over_all)), _stream())
     return (gates, ids, weights) if want_chosen else gates
 
 
-def router_choose_(logits: torch.Tensor, top: int, want_chosen: bool = False):
+def router_choose_(logits: torch.Tensor, top: int, want_chosen: bool = False, over_all: bool = False):
     """The choice alone: ``logits`` [T, experts] (float32, as a product left them) become the routing weights in place
     (see ``router_gates``).  Returns what ``router_gates`` returns."""
     _need_cuda(logits)
@@ -557,7 +712,7 @@ def router_choose_(logits: torch.Tensor, top: int, want_chosen: bool = False):
     tokens, experts = logits.shape
     ids = torch.empty((tokens, top), dtype=torch.int32, device=logits.device) if want_chosen else None
     weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device) if want_chosen else None
-    _call("kirai_router_choose", _ptr(logits), _ptr(ids), _ptr(weights), _i(tokens), _i(experts), _i(top), _stream())
+    _call("kirai_router_choose", _ptr(logits), _ptr(ids), _ptr(weights), _i(tokens), _i(experts), _i(top), _i(int(over_all)), _stream())
     return (logits, ids, weights) if want_chosen else logits
 
 
@@ -701,19 +856,32 @@ def qk_norm_rope_kv_write_(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_
 
 
 # --------------------------------------------------------------------- attention
-def mask_code(window: Optional[int], chunk: Optional[int] = None) -> int:
+MASK_KEEP_SHIFT = 20  # as in common.cuh
+
+
+def mask_code(window: Optional[int], chunk: Optional[int] = None, keep_first: int = 0) -> int:
     """How the kernels are told which keys a query sees: 0 every key up to its own position, W > 0 the last W of
-    them, -C < 0 those of its own chunk of C positions (chunks counted from position 0 of the sequence)."""
+    them, -C < 0 those of its own chunk of C positions (chunks counted from position 0 of the sequence).  A window
+    under which the sequence's first F keys stay visible to every later position is W + (F << 20)."""
     if window and chunk:
         raise KernelError("a layer has a window or a chunked mask, not both")
+    if keep_first:
+        if not window:
+            raise KernelError("kept first keys go with a window")
+        if not (0 < window < (1 << MASK_KEEP_SHIFT) and 0 < keep_first < (1 << 11)):
+            raise KernelError(f"a window of {window} keys that keeps the first {keep_first} is outside what the kernels take "
+                              f"(window below {1 << MASK_KEEP_SHIFT}, kept keys below {1 << 11})")
+        return int(window) + (int(keep_first) << MASK_KEEP_SHIFT)
+    if window and window >= (1 << MASK_KEEP_SHIFT):
+        raise KernelError(f"a window of {window} keys is outside what the kernels take (below {1 << MASK_KEEP_SHIFT})")
     return -int(chunk) if chunk else int(window or 0)
 
 
-def _attention_detail(q_heads: int, kv_heads: int, head_dim: int, window: Optional[int], chunk: Optional[int]) -> str:
+def _attention_detail(q_heads: int, kv_heads: int, head_dim: int, window: Optional[int], chunk: Optional[int], keep_first: int = 0) -> str:
     """What a launch timer's record says of an attention launch beside its entry point (nothing when no timer runs)."""
     if _timer is None:
         return ""
-    return f" heads={q_heads} kv={kv_heads} d={head_dim} mask={mask_code(window, chunk)}"
+    return f" heads={q_heads} kv={kv_heads} d={head_dim} mask={mask_code(window, chunk, keep_first)}"
 
 
 def _capped(name: str, softcap: Optional[float]):
@@ -725,7 +893,7 @@ def _capped(name: str, softcap: Optional[float]):
 
 def paged_attention_plain(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                           request_of_token: torch.Tensor, positions: torch.Tensor, window: Optional[int],
-                          scale: float, chunk: Optional[int] = None, softcap: Optional[float] = None) -> torch.Tensor:
+                          scale: float, chunk: Optional[int] = None, softcap: Optional[float] = None, keep_first: int = 0) -> torch.Tensor:
     """Causal grouped-query attention of ``q`` [T, nq, d] over the paged cache; returns [T, nq * d].  ``chunk``: a
     query sees the keys of its own chunk of that many positions only; ``softcap`` c: scores become c tanh(score / c)."""
     _need_cuda(q, cache, block_table, request_of_token, positions)
@@ -736,8 +904,8 @@ def paged_attention_plain(q: torch.Tensor, cache: torch.Tensor, block_table: tor
     name, cap = _capped(f"kirai_paged_attention_plain_{_suffix(q.dtype)}", softcap)
     _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(block_table),
           _ptr(request_of_token), _ptr(positions), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride),
-          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap,
-          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk))
+          _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk, keep_first)), _f(scale), *cap,
+          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk, keep_first))
     return out
 
 
@@ -774,7 +942,7 @@ def attention_prefill_takes_tcgen05(q_heads: int, kv_heads: int, head_dim: int, 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, query_start: torch.Tensor,
                       context_len: torch.Tensor, max_query_len: int, window: Optional[int], scale: float,
                       tcgen05: Optional[bool] = None, out: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                      softcap: Optional[float] = None) -> torch.Tensor:
+                      softcap: Optional[float] = None, keep_first: int = 0) -> torch.Tensor:
     """bf16 tensor-core attention for runs of new tokens (prompt portions, or any mix): q [T, nq, d].
     ``query_start`` holds rows of ``q`` and of the result, so the requests given may be a part of a larger batch
     (``out`` is then the whole batch's result, of which only their rows are written).  ``tcgen05`` picks the kernel (None: the tcgen05 kernel where it takes the shape, else the
@@ -793,8 +961,8 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
     name, cap = _capped("kirai_attention_prefill_tc_bf16" if tcgen05 else "kirai_attention_prefill_bf16", softcap)
     _call(name, _ptr(q), _ptr(cache), _ptr(out),
           _ptr(block_table), _ptr(query_start), _ptr(context_len), _i(requests), _i(max_query_len), _i(q_heads), _i(kv_heads),
-          _i(head_dim), _l(q_stride), _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale),
-          *cap, _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk))
+          _i(head_dim), _l(q_stride), _i(page_size), _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk, keep_first)), _f(scale),
+          *cap, _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk, keep_first))
     return out
 
 
@@ -888,7 +1056,7 @@ def decode_plan(context_lens, kv_heads: int, window: Optional[int] = None, tile:
 
 def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
                      window: Optional[int], scale: float, num_splits: int = 1, out: Optional[torch.Tensor] = None,
-                     chunk: Optional[int] = None, softcap: Optional[float] = None) -> torch.Tensor:
+                     chunk: Optional[int] = None, softcap: Optional[float] = None, keep_first: int = 0) -> torch.Tensor:
     """bf16 tensor-core attention for a batch in which every request brings one token: q [R, nq, d] (row r of ``q``,
     of the tables and of the result belongs to request r; ``out`` may be the head of a larger result)."""
     _need_cuda(q, cache, block_table, context_len)
@@ -906,8 +1074,8 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
     name, cap = _capped("kirai_attention_decode_bf16", softcap)
     _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
-          _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap, _i(num_splits),
-          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk))
+          _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk, keep_first)), _f(scale), *cap, _i(num_splits),
+          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk, keep_first))
     return out
 
 
@@ -924,7 +1092,7 @@ def sm_count(device: torch.device) -> int:
 def attention_decode_balanced(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, context_len: torch.Tensor,
                               window: Optional[int], scale: float, ctas: Optional[int] = None,
                               out: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
-                              softcap: Optional[float] = None) -> torch.Tensor:
+                              softcap: Optional[float] = None, keep_first: int = 0) -> torch.Tensor:
     """The decode attention with the key tiles of all (request, kv head) pairs cut into ``ctas`` equal ranges
     (default: one per SM), so that every CTA reads the same number of keys whatever the batch looks like."""
     _need_cuda(q, cache, block_table, context_len)
@@ -940,13 +1108,13 @@ def attention_decode_balanced(q: torch.Tensor, cache: torch.Tensor, block_table:
     name, cap = _capped("kirai_attention_decode_balanced_bf16", softcap)
     _call(name, _ptr(q), _ptr(cache), _ptr(out), _ptr(partial), _ptr(block_table),
           _ptr(context_len), _i(rows), _i(q_heads), _i(kv_heads), _i(head_dim), _l(q_stride), _i(page_size),
-          _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk)), _f(scale), *cap, _i(ctas),
-          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk))
+          _i(block_table.shape[1]), _i(num_pages), _i(mask_code(window, chunk, keep_first)), _f(scale), *cap, _i(ctas),
+          _ptr(error_flag(q.device)), _stream(), detail=_attention_detail(q_heads, kv_heads, head_dim, window, chunk, keep_first))
     return out
 
 
 def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, batch, window: Optional[int],
-                    scale: float, chunk: Optional[int] = None, softcap: Optional[float] = None) -> torch.Tensor:
+                    scale: float, chunk: Optional[int] = None, softcap: Optional[float] = None, keep_first: int = 0) -> torch.Tensor:
     """Attention of the product path over the paged cache for the tokens of ``batch``
     (a kirai_b200.engine.batch.StepBatch).  float32 takes the plain kernel; bfloat16 takes the
     tensor-core kernels (the decode kernel when every request brings one token), or the plain
@@ -955,7 +1123,7 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     fast = attention_takes_tensor_cores(q.dtype, head_dim) and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
     if not fast:
         return paged_attention_plain(q, cache, block_table, batch.request_of_token, batch.positions, window, scale,
-                                     chunk, softcap)
+                                     chunk, softcap, keep_first)
     decode_rows = batch.num_requests if batch.decode_only else getattr(batch, "num_decode", 0)
     if decode_rows and q_heads // kv_heads <= 16:
         # The requests that bring one token stand first in the batch (the batch builder puts them there) and take the
@@ -963,23 +1131,23 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
         # write their rows of one result.  A prompt kernel alone would give a decoding request one CTA per kv head.
         out = torch.empty((q.shape[0], q_heads * head_dim), dtype=q.dtype, device=q.device)
         _decode_rows(q[:decode_rows], cache, block_table[:decode_rows], batch, decode_rows, window, scale, out[:decode_rows],
-                     chunk, softcap)
+                     chunk, softcap, keep_first)
         if decode_rows < batch.num_requests:
             attention_prefill(q, cache, block_table[decode_rows:], batch.query_start[decode_rows:], batch.context_len[decode_rows:],
-                              batch.max_query_len, window, scale, out=out, chunk=chunk, softcap=softcap)
+                              batch.max_query_len, window, scale, out=out, chunk=chunk, softcap=softcap, keep_first=keep_first)
         return out
     return attention_prefill(q, cache, block_table, batch.query_start, batch.context_len, batch.max_query_len, window, scale,
-                             chunk=chunk, softcap=softcap)
+                             chunk=chunk, softcap=softcap, keep_first=keep_first)
 
 
 def _decode_rows(q, cache, block_table, batch, rows: int, window: Optional[int], scale: float, out: torch.Tensor,
-                 chunk: Optional[int] = None, softcap: Optional[float] = None) -> None:
+                 chunk: Optional[int] = None, softcap: Optional[float] = None, keep_first: int = 0) -> None:
     """The decode attention of the first ``rows`` requests of ``batch`` (one token each)."""
     kv_heads = cache.shape[2]
-    mask = dict(chunk=chunk, softcap=softcap)
+    mask = dict(chunk=chunk, softcap=softcap, keep_first=keep_first)
     if chunk:
         window = None
-    reach = window or chunk  # the most keys a token sees: what the launch is planned for
+    reach = (window + keep_first if window else None) or chunk  # the most keys a token sees: what the launch is planned for
     room = decode_cluster_room(q.device, q.shape[2], q.shape[1] // kv_heads)
     context_len = batch.context_len[:rows]
     # the batch may say which kernel (a captured step does: its lengths change between replays); otherwise

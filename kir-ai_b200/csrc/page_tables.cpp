@@ -38,6 +38,7 @@ struct Request {
 struct Tables {
     int page_size = 0;
     std::vector<long> windows;  // per group, -1: keeps everything
+    std::vector<long> keep_first;  // per group: a window never gives back the pages of a request's first so many tokens
     std::vector<Pool> pools;
     std::vector<int> free_slots;
     std::vector<char> slot_held;
@@ -57,6 +58,7 @@ KIRAI_HOST_EXPORT void* kirai_pages_create(int num_groups, const long* windows, 
     for (int g = 0; g < num_groups; ++g) {
         if (num_pages[g] <= 0) { delete t; return nullptr; }
         t->windows.push_back(windows[g]);
+        t->keep_first.push_back(0);
         Pool pool;
         pool.num_pages = num_pages[g];
         pool.held.assign(num_pages[g], 0);
@@ -136,7 +138,16 @@ KIRAI_HOST_EXPORT int kirai_pages_reserve(void* handle, long key, long new_token
     return 1;
 }
 
-// Records `new_tokens` written tokens; windowed groups give back pages wholly before length - window + 1.
+// A windowed group whose layers keep a sequence's first `keep` tokens visible holds on to their pages.
+KIRAI_HOST_EXPORT int kirai_pages_set_keep_first(void* handle, int group, long keep) {
+    Tables& t = *static_cast<Tables*>(handle);
+    if (group < 0 || group >= (int)t.keep_first.size() || keep < 0) return -1;
+    t.keep_first[group] = keep;
+    return 0;
+}
+
+// Records `new_tokens` written tokens; windowed groups give back pages wholly before length - window + 1
+// (but never the pages that hold a kept first token).
 KIRAI_HOST_EXPORT int kirai_pages_commit(void* handle, long key, long new_tokens) {
     Tables& t = *static_cast<Tables*>(handle);
     auto it = t.live.find(key);
@@ -153,7 +164,7 @@ KIRAI_HOST_EXPORT int kirai_pages_commit(void* handle, long key, long new_tokens
         long dead = first_visible / t.page_size;
         if (dead > (long)request.tables[g].size()) dead = (long)request.tables[g].size();
         bool changed = false;
-        for (long p = 0; p < dead; ++p) {
+        for (long p = pages_for(t, t.keep_first[g]); p < dead; ++p) {
             const int page = request.tables[g][p];
             if (page == NO_PAGE) continue;
             Pool& pool = t.pools[g];

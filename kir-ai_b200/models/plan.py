@@ -16,19 +16,20 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..parts.base import Norm, Runtime, StreamCopy, WeightSpec
+from ..parts.base import Norm, Runtime, ScaledSum, StreamCopy, WeightSpec
 from ..parts.block import Block
 from ..parts.embedding import Embedding, OutputHead
 
 
 @dataclass(frozen=True)
 class LayerCall:
-    """Run ``block`` with cache layer ``cache`` (None: the mixer keeps nothing);
+    """Run ``block`` with cache layer ``cache`` (None: the mixer keeps nothing; a tuple of cache layers for a mixer
+    whose ``cache_need()`` is a tuple of needs, as two mixers side by side of which one keeps pages and one a state);
     ``write`` false reads what an earlier call wrote in the same step.  ``shift_cache`` is the cache layer of the
     block's token shift, where it has one (a state slot per request; every call has its own)."""
 
     block: int
-    cache: Optional[int] = None
+    cache: object = None
     write: bool = True
     shift_cache: Optional[int] = None
 
@@ -70,6 +71,17 @@ class ModelPlan:
                 continue
             if call.cache is None:
                 raise PlanError(f"order[{step}]: block {call.block}'s mixer needs a cache layer")
+            if isinstance(need, tuple):
+                # several needs: every one a cache layer of its own, written by this call
+                if not isinstance(call.cache, tuple) or len(call.cache) != len(need) or not call.write:
+                    raise PlanError(f"order[{step}]: block {call.block}'s mixer needs {len(need)} cache layers that it writes")
+                for layer, one in zip(call.cache, need):
+                    if layer in needs:
+                        raise PlanError(f"order[{step}]: cache layer {layer} is written by two calls")
+                    needs[layer] = one
+                continue
+            if isinstance(call.cache, tuple):
+                raise PlanError(f"order[{step}]: block {call.block}'s mixer needs one cache layer, {call.cache} are named")
             if call.write:
                 if call.cache in needs:
                     raise PlanError(f"order[{step}]: cache layer {call.cache} is written by two calls")
@@ -138,7 +150,10 @@ class DecoderModel:
             else:
                 resid = embedding.forward(batch.token_ids)
             for i, call in enumerate(order):
-                view = cache.layer_view(call.cache) if call.cache is not None else None
+                if isinstance(call.cache, tuple):
+                    view = tuple(cache.layer_view(layer) for layer in call.cache)
+                else:
+                    view = cache.layer_view(call.cache) if call.cache is not None else None
                 following = self.plan.blocks[order[i + 1].block] if i + 1 < len(order) else None
                 if nvtx:
                     nvtx.range_push(f"layer call {i}: block {call.block}, {batch.num_tokens} tokens")
@@ -155,6 +170,9 @@ class DecoderModel:
         """32-bit logits [len(rows), V] of the token rows ``rows`` (int32, on the device)."""
         if isinstance(delta, StreamCopy):
             delta = None  # the last block left the stream complete
+        if isinstance(delta, ScaledSum) and not getattr(self.plan.final_norm, "takes_scaled_sum", False):
+            self.rt.ops.add_scaled_into_residual(resid, delta.rows, delta.factor)
+            delta = None
         with self.rt.ops.chained_products(self._kernels_only):
             normed = self.plan.final_norm.add_forward_rows(resid, delta, rows)
             logits = self.plan.head.forward(normed)

@@ -35,6 +35,11 @@ turns a score s into c tanh(s / c) before the softmax; ``chunk`` C lets position
 the same run of C positions counted from the sequence's start (all keys stay cached); ``gate`` names a matrix
 [q_heads * value_dim, hidden]: the concatenated heads are multiplied by sigmoid(gate x) before the output
 projection (the matrix rides in the stacked q, k, v product); ``out_bias`` names a bias of the output projection.
+``head_gate`` names a matrix [q_heads, hidden] instead: ONE number per head, sigmoid(head_gate x)_h, multiplies head
+h's output (it rides in the stacked product too).  ``keep_first`` F goes with a ``window`` W: position i sees j <= i
+when i - j < W or j < F, so a sequence's first F keys stay visible at their true positions (the cache keeps their
+pages when the window gives the others back).  A ``RotaryEmbedding`` whose cosine and sine carry a factor
+(``amplitude``) is applied with it by the preparation kernel.
 """
 from __future__ import annotations
 
@@ -54,7 +59,7 @@ class GQAttention(Mixer):
                  names: Optional[Dict[str, str]] = None, value_dim: Optional[int] = None, bias: bool = False,
                  qk_norm_over: str = "head", out_dtype: Optional[torch.dtype] = None, head_factor: Optional[str] = None,
                  softcap: Optional[float] = None, chunk: Optional[int] = None, gate: Optional[str] = None,
-                 out_bias: Optional[str] = None):
+                 out_bias: Optional[str] = None, head_gate: Optional[str] = None, keep_first: int = 0):
         if q_heads % kv_heads:
             raise ValueError(f"{q_heads} query heads are not a multiple of {kv_heads} kv heads")
         if qk_norm_over not in ("head", "projection"):
@@ -82,11 +87,19 @@ class GQAttention(Mixer):
             raise ValueError("a soft cap or a chunked mask is not built for a layer that reads another layer's cache")
         self.head_factor_name = prefix + head_factor if head_factor else None
         self.gate_name = prefix + gate if gate else None
+        self.head_gate_name = prefix + head_gate if head_gate else None
+        self.keep_first = int(keep_first or 0)
+        if self.keep_first and not window:
+            raise ValueError("kept first keys go with a window")
+        if gate and head_gate:
+            raise ValueError("an output gate has a number per column or a number per head, not both")
+        if (self.keep_first or head_gate) and reads_only:
+            raise ValueError("kept first keys or a gate per head are not built for a layer that reads another layer's cache")
         self.out_bias_name = prefix + out_bias if out_bias else None
         self.head_factor = self.out_bias = None
         self.defer_output_bias = False  # a block whose next norm adds the bias sets this
-        shifted_rotation = isinstance(position, RotaryEmbedding) and position.offset != 0
-        self.wide = (bias or self.value_dim != head_dim or (qk_norm_eps is not None and qk_norm_over == "projection")
+        shifted_rotation = isinstance(position, RotaryEmbedding) and (position.offset != 0 or position.amplitude != 1.0)
+        self.wide = (head_gate is not None or self.keep_first > 0 or bias or self.value_dim != head_dim or (qk_norm_eps is not None and qk_norm_over == "projection")
                      or head_factor is not None or gate is not None or shifted_rotation or self.softcap is not None
                      or self.chunk is not None or out_bias is not None)
         self.norm_over_projection = qk_norm_eps is not None and qk_norm_over == "projection"
@@ -105,6 +118,8 @@ class GQAttention(Mixer):
             sources += [(prefix + n["k"], kv_heads * head_dim), (prefix + n["v"], kv_heads * self.value_dim)]
         if self.gate_name:
             sources.append((self.gate_name, q_heads * self.value_dim))
+        if self.head_gate_name:
+            sources.append((self.head_gate_name, q_heads))
         self.qkv = Linear(sources, hidden_size)
         self.out = Linear([(prefix + n["o"], hidden_size)], q_heads * self.value_dim,
                           column_groups=(q_heads, self.value_dim, self.pad_dim) if self.wide else None)
@@ -115,7 +130,8 @@ class GQAttention(Mixer):
 
     def cache_need(self):
         if self.wide:
-            return KVCacheNeed(self.kv_heads, self.pad_dim, self.window, key_dim=self.head_dim, value_dim=self.value_dim)
+            return KVCacheNeed(self.kv_heads, self.pad_dim, self.window, key_dim=self.head_dim, value_dim=self.value_dim,
+                               keep_first=self.keep_first)
         return KVCacheNeed(self.kv_heads, self.head_dim, self.window)
 
     @property
@@ -198,11 +214,15 @@ class GQAttention(Mixer):
             q = ops.qkv_rope_write(qkv, self.q_heads, nkv, self.head_dim, self.value_dim, self.pad_dim, self.q_bias, self.k_bias,
                                    self.v_bias, self.head_factor, rot.inv_freq if rot is not None else None,
                                    rot.offset if rot is not None else 0, rot.rotary_dim if rot is not None else 0,
-                                   cache.kv, table, batch.request_of_token, batch.positions, self.rt.dtype)
-            mixed = ops.paged_attention(q, cache.kv, table, batch, self.window, self.scale, chunk=self.chunk, softcap=self.softcap)
+                                   cache.kv, table, batch.request_of_token, batch.positions, self.rt.dtype,
+                                   rot_amplitude=rot.amplitude if rot is not None else 1.0)
+            mixed = ops.paged_attention(q, cache.kv, table, batch, self.window, self.scale, chunk=self.chunk, softcap=self.softcap,
+                                        keep_first=self.keep_first)
+            gate_at = self.q_heads * self.head_dim + nkv * (self.head_dim + self.value_dim)
             if self.gate_name:
-                gate_at = self.q_heads * self.head_dim + nkv * (self.head_dim + self.value_dim)
                 ops.sigmoid_gate_(mixed, qkv[:, gate_at:], self.q_heads, self.value_dim, self.pad_dim)
+            if self.head_gate_name:
+                ops.head_gate_(mixed, qkv[:, gate_at : gate_at + self.q_heads], self.q_heads, self.value_dim, self.pad_dim)
             return mixed
         q = ops.qkv_wide_norm_write(qkv, self.q_heads, nkv, self.head_dim, self.value_dim, self.pad_dim, self.q_bias,
                                     self.k_bias, self.v_bias, self.q_norm_weight, self.k_norm_weight, self.qk_norm_eps or 0.0,

@@ -36,7 +36,8 @@ class WeightSpec:
 @dataclass(frozen=True)
 class KVCacheNeed:
     """A mixer that keeps keys and values of earlier tokens in pages.
-    ``window`` None keeps every token; a width W keeps the last W.  ``head_dim`` is the width of a
+    ``window`` None keeps every token; a width W keeps the last W (and, with ``keep_first`` F, a request's first F
+    tokens for good: a window under which every position still sees the sequence's first tokens).  ``head_dim`` is the width of a
     cache row.  Keys and values may be narrower than the row and differ from each other
     (``key_dim``, ``value_dim``; None: the whole row): the columns beyond them are never written
     and stay zero, so kernels that read whole rows compute the same scores and sums."""
@@ -46,6 +47,7 @@ class KVCacheNeed:
     window: Optional[int] = None
     key_dim: Optional[int] = None
     value_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -87,6 +89,16 @@ class StreamCopy:
     sub-layer may read instead of rounding the stream again."""
 
     rows: Optional[torch.Tensor] = None
+
+
+@dataclass
+class ScaledSum:
+    """What a sub-layer leaves to be added into the stream when the block multiplies its sub-layers' outputs by a
+    constant: ``factor`` times the sum of ``rows`` (one or two float32 tensors [T, width]).  A norm that
+    ``takes_scaled_sum`` adds it in its own pass over the row; for any other the block adds it with a kernel first."""
+
+    rows: list
+    factor: float
 
 
 class Runtime:
@@ -214,3 +226,8 @@ class FeedForward(Part):
 
     def fuses_into_norm(self, rows: int) -> bool:
         return False
+
+    def forward_terms(self, x: torch.Tensor, batch) -> list:
+        """The output as tensors whose sum it is (a part with a branch that runs for every token beside its routed ones
+        leaves the addition to whoever adds the output into the stream); one term unless a part says otherwise."""
+        return [self.forward(x, batch)]

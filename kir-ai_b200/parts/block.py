@@ -21,6 +21,11 @@ A ``pre_norm`` block may carry a ``shift`` (``parts.shift.TokenShift``): what th
 mixed with the row of the token before.  The shift keeps a request's last row in a state slot of its own (the
 layer call's ``shift_cache``), the norm hands it 32-bit rows, and the first norm then stays a kernel.  A mixer whose
 output projection has a bias may leave it to the norm that adds its output into the stream (``deferred_bias``).
+
+``residual_scale`` m (``pre_norm`` only) multiplies what every sub-layer adds: h <- h + m * mixer(norm1(h)), then
+h <- h + m * ffn(norm2(h)).  The sub-layers then leave 32-bit rows (a feed-forward may leave several terms,
+``FeedForward.forward_terms``), which travel to the next norm as a ``ScaledSum``; a norm that ``takes_scaled_sum`` adds
+them in its own pass, for any other a kernel adds them first.  No norm is folded into a product on this path.
 """
 from __future__ import annotations
 
@@ -28,7 +33,7 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from .base import FeedForward, FusedNormSpec, Mixer, Norm, Part, Runtime, StreamCopy, UnscaledNorm, WeightSpec
+from .base import FeedForward, FusedNormSpec, Mixer, Norm, Part, Runtime, ScaledSum, StreamCopy, UnscaledNorm, WeightSpec
 
 ARRANGEMENTS = ("pre_norm", "parallel", "out_norm")
 
@@ -42,7 +47,10 @@ def _offers(part, method: str, rows: int) -> bool:
 
 class Block(Part):
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], arrangement: str = "pre_norm",
-                 shift: Optional[Part] = None):
+                 shift: Optional[Part] = None, residual_scale: Optional[float] = None):
+        if residual_scale is not None and (arrangement != "pre_norm" or shift is not None):
+            raise ValueError("a factor on the sub-layers' outputs is built for the pre_norm arrangement without a token shift")
+        self.residual_scale = None if residual_scale is None else float(residual_scale)
         if shift is not None and arrangement != "pre_norm":
             raise ValueError("a token shift is built for the pre_norm arrangement only")
         if arrangement not in ARRANGEMENTS:
@@ -96,7 +104,8 @@ class Block(Part):
     def entry_spec(self, rows: int) -> Optional[FusedNormSpec]:
         """What the block before needs to take over this block's first norm for a batch of ``rows`` tokens;
         None if the norm stays a kernel."""
-        if self.arrangement != "pre_norm" or self.shift is not None or not _offers(self.mixer, "takes_unscaled", rows):
+        if (self.arrangement != "pre_norm" or self.shift is not None or self.residual_scale is not None
+                or not _offers(self.mixer, "takes_unscaled", rows)):
             return None
         return self._spec(self.norm1)
 
@@ -113,6 +122,12 @@ class Block(Part):
         rows = resid.shape[0]
         if isinstance(delta, StreamCopy) and self.arrangement != "out_norm":
             delta = None  # the block before left nothing to add
+        if isinstance(delta, ScaledSum) and (self.arrangement != "pre_norm" or self.shift is not None
+                                             or not getattr(self.norm1, "takes_scaled_sum", False)):
+            self.rt.ops.add_scaled_into_residual(resid, delta.rows, delta.factor)
+            delta = None
+        if self.residual_scale is not None:
+            return self._forward_scaled(resid, delta, batch, cache, write_cache)
         if self.arrangement == "out_norm":
             return self._forward_out_norm(resid, delta, batch, cache, write_cache)
         if self.arrangement == "pre_norm":
@@ -144,6 +159,24 @@ class Block(Part):
         m = self.ffn.forward(n, batch)
         self.norm1.rt.ops.add_into_residual(resid, a)
         return resid, m
+
+    def _forward_scaled(self, resid, delta, batch, cache, write_cache):
+        """pre_norm with a factor on what the sub-layers add; their outputs are 32-bit rows."""
+        ops, scale = self.rt.ops, self.residual_scale
+        n1 = self.norm1.add_forward(resid, delta)
+        left = ScaledSum(self._wide([self.mixer.forward(n1, batch, cache, write_cache)]), scale)
+        if self.ffn is None:
+            return resid, left
+        if getattr(self.norm2, "takes_scaled_sum", False):
+            n2 = self.norm2.add_forward(resid, left)
+        else:
+            ops.add_scaled_into_residual(resid, left.rows, left.factor)
+            n2 = self.norm2.add_forward(resid, None)
+        return resid, ScaledSum(self._wide(self.ffn.forward_terms(n2, batch)), scale)
+
+    @staticmethod
+    def _wide(rows):
+        return [r if r.dtype == torch.float32 else r.float() for r in rows]
 
     def _forward_out_norm(self, resid, delta, batch, cache, write_cache):
         ops, narrow, rows = self.rt.ops, self.rt.dtype != torch.float32, resid.shape[0]

@@ -78,13 +78,15 @@ class Embedding(Part):
 
 
 class OutputHead(Part):
-    """Logits = W x in 32-bit, W [V, H] (its own tensor, or the embedding table when tied)."""
+    """Logits = W x in 32-bit, W [V, H] (its own tensor, or the embedding table when tied).  ``softcap`` c turns a
+    logit z into c tanh(z / c)."""
 
     capture_safe = True
     kernels_only = True
 
-    def __init__(self, weight_name: str, vocab_size: int, hidden_size: int):
+    def __init__(self, weight_name: str, vocab_size: int, hidden_size: int, softcap: Optional[float] = None):
         self.weight_name, self.vocab_size, self.hidden_size = weight_name, vocab_size, hidden_size
+        self.softcap = float(softcap) if softcap else None
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
@@ -95,4 +97,5 @@ class OutputHead(Part):
         self.weight = _table(weights, rt, self.weight_name, self.hidden_size)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.rt.ops.linear(x, self.weight, torch.float32)
+        logits = self.rt.ops.linear(x, self.weight, torch.float32)
+        return self.rt.ops.softcap_(logits, self.softcap) if self.softcap else logits

@@ -26,6 +26,14 @@ with its expert's matrices, and a combine kernel sums each token's rows with
 its routing weights in 32-bit.  Only the chosen experts' arithmetic is done.
 This path keeps a second copy of the down matrices, stacked along the output
 axis.  Neither path waits for the host.
+
+Options.  ``activation="silu_gated"``: an expert is down(silu(gate x) * (up x)) with a gate matrix of its own; the
+experts' gate and up matrices are stacked expert by expert ([gate_e; up_e]), the few-token kernel applies the gated
+activation and the routing weight together, and the many-token path runs the grouped product without an epilogue and
+the framework's gated-activation kernel on its rows.  ``scoring="softmax_all"``: the weights are the chosen experts'
+shares of the softmax over ALL experts' logits, not renormalised (the choice is the same: the largest logits).
+``shared``: a feed-forward that runs for every token beside the routed experts; its output is added (``forward_terms``
+hands both terms to whoever adds them into the stream).
 """
 from __future__ import annotations
 
@@ -36,7 +44,8 @@ import torch
 from .base import FeedForward, Runtime, WeightSpec
 from .linear import Linear
 
-ACTIVATIONS = ("relu2",)
+ACTIVATIONS = ("relu2", "silu_gated")
+SCORINGS = ("softmax_chosen", "softmax_all")
 GROUPED_MIN_ROWS = 512  # pairs of (token, chosen expert) from which a step sorts them by expert
 
 
@@ -46,18 +55,29 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, prefix: str, hidden_size: int, expert_size: int, experts: int, top: int, *,
                  activation: str = "relu2", names: Optional[Dict[str, str]] = None,
-                 out_dtype: Optional[torch.dtype] = None):
+                 out_dtype: Optional[torch.dtype] = None, scoring: str = "softmax_chosen", shared: Optional[FeedForward] = None):
         if activation not in ACTIVATIONS:
             raise ValueError(f"unknown expert activation {activation!r}; known: {ACTIVATIONS}")
+        if scoring not in SCORINGS:
+            raise ValueError(f"unknown router scoring {scoring!r}; known: {SCORINGS}")
+        self.gated = activation == "silu_gated"
+        self.over_all = scoring == "softmax_all"
+        self.shared = shared
         if not 0 < top <= experts:
             raise ValueError(f"every token uses {top} of {experts} experts")
-        n = {"router": "router.weight", "up": "experts.{e}.up_proj.weight", "down": "experts.{e}.down_proj.weight"}
+        n = {"router": "router.weight", "up": "experts.{e}.up_proj.weight", "down": "experts.{e}.down_proj.weight",
+             "gate": "experts.{e}.gate_proj.weight"}
         n.update(names or {})
         self.hidden_size, self.expert_size, self.experts, self.top = hidden_size, expert_size, experts, top
         self.activation = activation
         self.out_dtype = out_dtype
         self.router_name = prefix + n["router"]
-        self.up = Linear([(prefix + n["up"].format(e=e), expert_size) for e in range(experts)], hidden_size)
+        if self.gated:
+            # expert by expert: its gate rows, then its up rows
+            self.up = Linear([(prefix + n[kind].format(e=e), expert_size) for e in range(experts) for kind in ("gate", "up")],
+                             hidden_size)
+        else:
+            self.up = Linear([(prefix + n["up"].format(e=e), expert_size) for e in range(experts)], hidden_size)
         self.down = Linear([(prefix + n["down"].format(e=e), expert_size) for e in range(experts)], hidden_size,
                            side_by_side=True)
         self.down_stacked = Linear([(prefix + n["down"].format(e=e), hidden_size) for e in range(experts)], expert_size)
@@ -66,14 +86,25 @@ class RoutedExperts(FeedForward):
         self.grouped = False
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
+        shared = self.shared.weight_specs() if self.shared is not None else {}
         return {self.router_name: WeightSpec((self.experts, self.hidden_size), "linear"),
-                **self.up.weight_specs(), **self.down.weight_specs()}
+                **self.up.weight_specs(), **self.down.weight_specs(), **shared}
+
+    @property
+    def capture_safe(self) -> bool:
+        return self.shared is None or bool(getattr(self.shared, "capture_safe", False))
+
+    @property
+    def kernels_only(self) -> bool:
+        return self.shared is None or bool(getattr(self.shared, "kernels_only", False))
 
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
         self.router = weights.on_device(self.router_name, torch.float32)
         self.up.load(weights, rt)
         self.down.load(weights, rt)
+        if self.shared is not None:
+            self.shared.load(weights, rt)
         # sorting by expert pays only where a token uses a part of the experts, and needs whole 128-row boxes per expert
         self.grouped = (rt.dtype == torch.bfloat16 and self.top < self.experts and self.expert_size % 128 == 0
                         and self.hidden_size % 128 == 0 and hasattr(rt.ops, "linear_grouped"))
@@ -90,8 +121,8 @@ class RoutedExperts(FeedForward):
     def _route(self, x: torch.Tensor, want_chosen: bool):
         ops = self.rt.ops
         if self.router_product is not None and x.shape[0] >= self.ROUTER_PRODUCT_MIN_ROWS:
-            return ops.router_choose_(self.router_product.forward(x, torch.float32), self.top, want_chosen)
-        return ops.router_gates(x, self.router, self.top, want_chosen)
+            return ops.router_choose_(self.router_product.forward(x, torch.float32), self.top, want_chosen, over_all=self.over_all)
+        return ops.router_gates(x, self.router, self.top, want_chosen, over_all=self.over_all)
 
     def _sorts(self, rows: int) -> bool:
         return self.grouped and rows * self.top >= GROUPED_MIN_ROWS
@@ -102,20 +133,36 @@ class RoutedExperts(FeedForward):
         _, ids, mix = self._route(x, True)
         tile_group, slot_of, row_of_slot = ops.route_plan(ids, self.experts)
         rows = ops.route_gather(x, row_of_slot)
-        hidden = ops.linear_grouped(rows, self.up.weight, self.experts, tile_group, relu2=True)
+        if self.gated:
+            hidden = ops.gated_activation(ops.linear_grouped(rows, self.up.weight, self.experts, tile_group), "silu")
+        else:
+            hidden = ops.linear_grouped(rows, self.up.weight, self.experts, tile_group, relu2=True)
         return ops.linear_grouped(hidden, self.down_stacked.weight, self.experts, tile_group), slot_of, mix
 
     def adds_normed(self, rows: int) -> bool:
         """Optional, for a block that norms this part's OUTPUT: whether, for a batch of ``rows`` tokens, the part has
         ``forward_add_normed(x, batch, resid, spec)``, which adds the normed output into the 32-bit stream itself (the
         weighted sum of a token's expert rows is then never written out) and returns the stream's runtime-dtype copy."""
-        return self._sorts(rows) and self.rt.ops.route_combine_norm_add_takes(self.hidden_size)
+        return self.shared is None and self._sorts(rows) and self.rt.ops.route_combine_norm_add_takes(self.hidden_size)
 
     def forward_add_normed(self, x: torch.Tensor, batch, resid: torch.Tensor, spec):
         y, slot_of, mix = self._sorted_rows(x)
         return self.rt.ops.route_combine_norm_add(resid, y, slot_of, mix, spec.weight, spec.eps, self.rt.dtype)
 
+    def forward_terms(self, x: torch.Tensor, batch=None) -> list:
+        """[the routed experts' weighted sum] and, with a shared branch, [.., its output]."""
+        routed = self._forward_routed(x, batch)
+        return [routed] if self.shared is None else [routed, self.shared.forward(x, batch)]
+
     def forward(self, x: torch.Tensor, batch=None) -> torch.Tensor:
+        if self.shared is None:
+            return self._forward_routed(x, batch)
+        if self.out_dtype != torch.float32:
+            raise ValueError("experts with a shared branch leave 32-bit rows (out_dtype=torch.float32), which are added in 32-bit")
+        routed, shared = self.forward_terms(x, batch)
+        return self.rt.ops.add_scaled_into_residual(routed, [shared if shared.dtype == torch.float32 else shared.float()], 1.0)
+
+    def _forward_routed(self, x: torch.Tensor, batch=None) -> torch.Tensor:
         ops = self.rt.ops
         if self._sorts(x.shape[0]):
             y, slot_of, mix = self._sorted_rows(x)
@@ -123,5 +170,8 @@ class RoutedExperts(FeedForward):
             return out if self.out_dtype == torch.float32 else ops.round_rows(out)
         gates = self._route(x, False)
         hidden = self.up.forward(x)
-        ops.relu2_gate_(hidden, gates, self.expert_size)
+        if self.gated:
+            hidden = ops.gated_expert_gate(hidden, gates, self.expert_size, "silu")
+        else:
+            ops.relu2_gate_(hidden, gates, self.expert_size)
         return self.down.forward(hidden, self.out_dtype)

@@ -11,7 +11,7 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import FusedNormSpec, Norm, Runtime, WeightSpec
+from .base import FusedNormSpec, Norm, Runtime, ScaledSum, WeightSpec
 
 
 class RMSNorm(Norm):
@@ -90,3 +90,51 @@ class LayerNorm(Norm):
     def add_forward_rows(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """The norm of ``resid[rows] + delta[rows]`` only; the stream is left untouched."""
         return self.rt.ops.add_layernorm(resid, delta, self.weight, self.eps, self.rt.dtype, row_index=rows)
+
+
+class DynamicTanh(Norm):
+    """Dynamic Tanh in the place of a norm: y = tanh(alpha * x) * weight + bias, element by element, with a learned
+    scalar ``alpha``; no mean or variance of the row is taken.  The tensors are ``<name>`` (weight), ``<name>.alpha``
+    (a scalar) and ``<name>.b``.  ``add_forward`` adds what the sub-layer before left (a tensor, or a ``ScaledSum``)
+    into the 32-bit stream in the same pass.  A kernel of its own: there is no 1 / rms factor a product could take
+    over."""
+
+    capture_safe = True
+    kernels_only = True
+    takes_scaled_sum = True
+
+    def __init__(self, weight_name: str, width: int, alpha_name: Optional[str] = None, bias_name: Optional[str] = None):
+        self.weight_name, self.width = weight_name, width
+        self.alpha_name = alpha_name or weight_name + ".alpha"
+        self.bias_name = bias_name or weight_name + ".b"
+        self.weight = self.alpha = self.bias = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.width,), "norm"), self.alpha_name: WeightSpec((), "norm"),
+                self.bias_name: WeightSpec((self.width,), "bias")}
+
+    def load(self, weights, rt: Runtime) -> None:
+        self.rt = rt
+        self.weight = weights.on_device(self.weight_name, torch.float32)
+        self.alpha = weights.on_device(self.alpha_name, torch.float32).reshape(1).contiguous()
+        self.bias = weights.on_device(self.bias_name, torch.float32)
+
+    @staticmethod
+    def _terms(delta):
+        if delta is None:
+            return [], 1.0
+        if isinstance(delta, ScaledSum):
+            return list(delta.rows), float(delta.factor)
+        return [delta if delta.dtype == torch.float32 else delta.float()], 1.0
+
+    def add_forward(self, resid: torch.Tensor, delta=None) -> torch.Tensor:
+        rows, factor = self._terms(delta)
+        return self.rt.ops.add_dyt(resid, rows, factor, self.alpha, self.weight, self.bias, self.rt.dtype)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.rt.ops.add_dyt(x, [], 1.0, self.alpha, self.weight, self.bias, self.rt.dtype)
+
+    def add_forward_rows(self, resid: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        """The rows ``rows`` of the stream plus what is left to add, through the form; the stream is left untouched."""
+        terms, factor = self._terms(delta)
+        return self.rt.ops.add_dyt(resid, terms, factor, self.alpha, self.weight, self.bias, self.rt.dtype, row_index=rows)

@@ -10,6 +10,13 @@ frequency stays where l < original / high, becomes f / factor where l > original
 (1 - s) f / factor + s f with s = (original / l - low) / (high - low).  ``offset`` rotates columns [offset, offset +
 rotary_dim) of a head instead of its first ones.  With either option the table is worked out in 64-bit and rounded
 once.
+
+A second kind of ``scaling`` (keys ``factor``, ``original``, ``fast``, ``slow``; the rule known as YaRN) stretches by
+the INDEX of a frequency: with dim(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), the index at which a
+wavelength makes t turns over ``original`` positions, lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)),
+rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency becomes
+f_i / factor * ramp_i + f_i * (1 - ramp_i), and cosine and sine are multiplied by ``amplitude`` = 0.1 ln(factor) + 1
+(the attention preparation kernel takes that factor; ``apply`` alone does not rotate with it).
 """
 from __future__ import annotations
 
@@ -33,7 +40,16 @@ class RotaryEmbedding(PositionEncoding):
         self.theta = float(theta)
         self.offset = offset
         self.scaling = None
-        if scaling is not None:
+        self.ramp = None
+        self.amplitude = 1.0
+        if scaling is not None and "fast" in scaling:
+            import math
+
+            self.ramp = {key: float(scaling[key]) for key in ("factor", "original", "fast", "slow")}
+            if min(self.ramp.values()) <= 0.0 or self.theta <= 1.0:
+                raise ValueError(f"frequency scaling by index needs positive constants and a base above one, got {scaling}")
+            self.amplitude = 0.1 * math.log(self.ramp["factor"]) + 1.0
+        elif scaling is not None:
             self.scaling = {key: float(scaling[key]) for key in ("factor", "low", "high", "original")}
             if self.scaling["high"] == self.scaling["low"] or self.scaling["factor"] <= 0.0:
                 raise ValueError(f"frequency scaling needs high != low and a positive factor, got {scaling}")
@@ -60,6 +76,16 @@ class RotaryEmbedding(PositionEncoding):
             between = (1.0 - smooth) * freq / sc["factor"] + smooth * freq
             freq = torch.where(wavelength < sc["original"] / sc["high"], freq,
                                torch.where(wavelength > sc["original"] / sc["low"], freq / sc["factor"], between))
+        if self.ramp is not None:
+            r = self.ramp
+
+            def index_of(turns: float) -> float:
+                return self.rotary_dim * math.log(r["original"] / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(index_of(r["fast"])), 0)
+            hi = min(math.ceil(index_of(r["slow"])), self.rotary_dim - 1)
+            ramp = torch.clamp((index - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            freq = freq / r["factor"] * ramp + freq * (1.0 - ramp)
         return freq.to(torch.float32)
 
     def load(self, weights, rt: Runtime) -> None:
@@ -67,6 +93,8 @@ class RotaryEmbedding(PositionEncoding):
         self.inv_freq = self.frequencies().to(rt.device)
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        if self.amplitude != 1.0:
+            raise ValueError("a rotation whose cosine and sine carry a factor runs inside the attention preparation only")
         if self.offset:
             raise ValueError("a rotation that does not start at a head's first column runs inside the attention preparation only")
         self.rt.ops.rope_(q, positions, self.inv_freq, self.rotary_dim)

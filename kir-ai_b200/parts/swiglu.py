@@ -20,10 +20,12 @@ class SwiGLU(FeedForward):
 
     activation = "silu"
 
-    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, names: Optional[Dict[str, str]] = None):
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, names: Optional[Dict[str, str]] = None,
+                 out_dtype: Optional[torch.dtype] = None):
         n = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
         n.update(names or {})
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.out_dtype = out_dtype  # of the result (default: the runtime's)
         self.gate_up = Linear([(prefix + n["gate"], intermediate_size), (prefix + n["up"], intermediate_size)], hidden_size)
         self.down = Linear([(prefix + n["down"], hidden_size)], intermediate_size)
 
@@ -51,7 +53,7 @@ class SwiGLU(FeedForward):
         return self.fused_weight is not None and self.down.fuses_norms(rows)
 
     def forward(self, x, batch=None) -> torch.Tensor:
-        return self.down.forward(self._activation(x))
+        return self.down.forward(self._activation(x), self.out_dtype)
 
     def forward_into_norm(self, x, batch, resid, spec):
         return self.down.forward_into_norm(self._activation(x), resid, spec)
@@ -74,8 +76,8 @@ class GatedMLP(SwiGLU):
     """The same feed-forward with the activation as an argument (``silu`` or ``gelu_tanh``)."""
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, out_dtype: Optional[torch.dtype] = None):
         if activation not in ("silu", "gelu_tanh"):
             raise ValueError(f"unknown activation {activation!r}; known: silu, gelu_tanh")
-        super().__init__(prefix, hidden_size, intermediate_size, names)
+        super().__init__(prefix, hidden_size, intermediate_size, names, out_dtype)
         self.activation = activation

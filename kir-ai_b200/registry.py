@@ -72,6 +72,10 @@ def _register_builtin() -> None:
     from .models.silupel import build_silupel_plan
 
     register_architecture(SilupelConfig.architecture, SilupelConfig, build_silupel_plan, replace=True)
+    from .config.figalix import FigalixConfig
+    from .models.figalix import build_figalix_plan
+
+    register_architecture(FigalixConfig.architecture, FigalixConfig, build_figalix_plan, replace=True)
 
 
 _register_builtin()
