@@ -277,6 +277,34 @@ def silupel_config(size: dict, layers: int, intermediate: int) -> dict:
             "layers": [{"type": kinds[i % 4][0], "mixer": dict(kinds[i % 4][1]), "mlp": dict(mlp)} for i in range(layers)]}
 
 
+FP32_PEAK = 148 * 128 * 2 * 1.965e9  # nominal: 128 32-bit multiply-adds a clock on each of 148 processors at the highest clock
+
+
+FIGALIX_STATE = dict(vdim=64, state=128, conv=4)   # state-space heads of 64 columns with 128 state rows, inner = 2 width
+FIGALIX_MEMORY = dict(dim=128, vdim=256)            # matrix-memory heads, width / 256 of them
+FIGALIX_WINDOW = dict(size=1024, keep_first=4)
+
+
+def figalix_config(size: dict, layers: int, intermediate: int) -> dict:
+    """A Figalix config.json of one size: layers in the order state space, side by side (and so on); the state-space
+    mixer twice as wide as the model with one group; the attention side with the size's heads, half of each head
+    rotated (frequencies stretched by index), a window of 1,024 that keeps four first keys; the memory side with
+    width / 256 heads of 128 x 256; feed-forwards in the order dense (as large as the dense model's), experts (the
+    size's, with a shared branch as large as one expert)."""
+    width = size["width"]
+    state = {"heads": 2 * width // FIGALIX_STATE["vdim"], "vdim": FIGALIX_STATE["vdim"], "state": FIGALIX_STATE["state"], "groups": 1,
+             "conv": FIGALIX_STATE["conv"], "norm_groups": 1}
+    left = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["vdim"], "scale": size["dim"] ** -0.5,
+            "rot": {"base": 500000.0, "dims": size["dim"] // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}},
+            "mask": dict(FIGALIX_WINDOW)}
+    right = {"heads": width // 256, "dim": FIGALIX_MEMORY["dim"], "vdim": FIGALIX_MEMORY["vdim"], "gate_cap": 15.0}
+    mixers = [("mamba2", state), ("parallel", {"left": left, "right": right})]
+    mlps = [{"kind": "dense", "ff": intermediate},
+            {"kind": "moe", "router": {"experts": size["experts"], "top": size["top"]}, "expert": {"ff": size["ff"]}, "shared": {"ff": size["ff"]}}]
+    return {"architecture": "Figalix", "width": width, "vocab": size["vocab"], "norm": {"eps": 1e-6}, "residual_mult": 0.5, "logit_softcap": 30.0,
+            "layers": [{"type": mixers[i % 2][0], "mixer": dict(mixers[i % 2][1]), "mlp": dict(mlps[i % 2])} for i in range(layers)]}
+
+
 def design_configs(size: dict, layers: int):
     """(Zoferax config.json, Qwen3 config.json, Silupel config.json) of one size: the same width, heads and layer count;
     the dense feed-forward is as large as the experts that one token uses (3 I H = 2 top ff H)."""
@@ -289,23 +317,24 @@ def design_configs(size: dict, layers: int):
                  num_hidden_layers=layers, num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"],
                  head_dim=size["dim"], vocab_size=size["vocab"], max_position_embeddings=40960, rms_norm_eps=1e-6,
                  rope_theta=1000000.0, tie_word_embeddings=False)
-    return {"zoferax": zoferax, "qwen3-dense": dense, "silupel": silupel_config(size, layers, intermediate)}
+    return {"zoferax": zoferax, "qwen3-dense": dense, "silupel": silupel_config(size, layers, intermediate),
+            "figalix": figalix_config(size, layers, intermediate)}
 
 
 def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: float, size: dict, design: str, peaks,
-                 visible=None) -> list:
+                 visible=None, requests: int = 1) -> list:
     """One row per entry point of a step: time, the work the DESIGN asks for (not what the kernel chose to compute), and
     that work over the time as a fraction of the measured peak (bytes over the copy bandwidth or flops over the bf16
     rate, whichever is the greater)."""
     import re
 
     width, heads, kvh, dk = size["width"], size["heads"], size["kv_heads"], size["dim"]
-    dv = size["vdim"] if design in ("zoferax", "silupel") else dk
+    dv = size["vdim"] if design in ("zoferax", "silupel", "figalix") else dk
     visible = visible or (lambda mask: (context_pairs, cache_rows))
     routed = size["experts"] * size["ff"]
     rows = []
     for name, (count, ms) in sorted(summary.items(), key=lambda item: -item[1][1]):
-        flops = bytes_ = 0.0
+        flops = bytes_ = simt = 0.0
         label = name
         match = re.search(r"m=(\d+) n=(\d+) k=(\d+) form=(\d+)", name)
         if match and "grouped" in name:
@@ -334,6 +363,29 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
         elif "attention" in name:
             flops = 2.0 * heads * (dk + dv) * context_pairs * count
             bytes_ = (2.0 * kvh * (dk + dv) * cache_rows + 2.0 * tokens * heads * (dk + dv)) * count
+        elif "ssm_walk" in name or "matrix_memory_walk" in name:
+            # a walk: every token touches the whole state of every head once (decay, outer product, read-out), in 32-bit
+            # on the ordinary pipe; a request's state is read and written once a step
+            if "ssm" in name:
+                cells = (2 * width // FIGALIX_STATE["vdim"]) * FIGALIX_STATE["vdim"] * FIGALIX_STATE["state"]
+                cols = 2 * width + 2 * FIGALIX_STATE["state"] + 2 * width // FIGALIX_STATE["vdim"] + 2 * width
+            else:
+                cells = (width // 256) * FIGALIX_MEMORY["dim"] * FIGALIX_MEMORY["vdim"]
+                cols = (width // 256) * (2 * FIGALIX_MEMORY["dim"] + 2 * FIGALIX_MEMORY["vdim"] + 2)
+            simt = 6.0 * tokens * cells * count
+            bytes_ = (4.0 * tokens * cols + 8.0 * cells * requests) * count
+        elif "conv_silu" in name:
+            bytes_ = tokens * (2 * width + 2 * FIGALIX_STATE["state"]) * 8.0 * count
+        elif "gated_group_norm" in name:
+            bytes_ = tokens * 2 * width * 10.0 * count
+        elif "rms_pair_mean" in name:
+            bytes_ = tokens * width * 12.0 * count
+        elif "add_dyt" in name or "add_scaled" in name:
+            bytes_ = tokens * width * 16.0 * count
+        elif "head_gate" in name:
+            bytes_ = tokens * heads * dv * 4.0 * count
+        elif "gated_expert_gate" in name:
+            bytes_ = tokens * routed * 6.0 * count
         elif "qkv_wide_norm" in name:
             cols = heads * dk + kvh * (dk + dv)
             bytes_ = tokens * (4.0 * cols + 2.0 * cols) * count
@@ -364,9 +416,10 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
         elif "embedding" in name or "round_rows" in name:
             bytes_ = tokens * width * 6.0 * count
         seconds = ms / 1e3
-        frac = max(bytes_ / (peaks["hbm_gbs"] * 1e9), flops / (peaks["bf16_tflops"] * 1e12)) / seconds if seconds > 0 else 0.0
-        rows.append({"kernel": label, "launches": count, "ms": round(ms, 4), "frac_of_measured_peak": round(frac, 3),
-                     "bound": "flops" if flops / (peaks["bf16_tflops"] * 1e12) > bytes_ / (peaks["hbm_gbs"] * 1e9) else "bytes"})
+        ideal = {"bytes": bytes_ / (peaks["hbm_gbs"] * 1e9), "flops": flops / (peaks["bf16_tflops"] * 1e12), "fp32": simt / FP32_PEAK}
+        bound = max(ideal, key=ideal.get)
+        frac = ideal[bound] / seconds if seconds > 0 else 0.0
+        rows.append({"kernel": label, "launches": count, "ms": round(ms, 4), "frac_of_measured_peak": round(frac, 3), "bound": bound})
     return rows
 
 
@@ -422,15 +475,21 @@ def compare_designs(args) -> int:
             pages = runner.cache.open(("prefill", "timed"))
             with ops.launch_timer() as timer:
                 runner.step([StepEntry(pages, prompt(T), [T - 1])], check_errors=False)
+            def seen(p, mask):
+                # how many keys position p sees: its chunk's, all up to itself, or its window's and the kept first ones
+                if mask < 0:
+                    return p % -mask + 1
+                if mask == 0:
+                    return p + 1
+                window, kept = mask & ((1 << 20) - 1), mask >> 20
+                return min(p + 1, window) + max(0, min(kept, p + 1 - window))
+
             def prefill_visible(mask):
                 # pairs of (query, key it sees) and key rows read, for a prompt of T tokens from position 0
-                if mask < 0:
-                    return float(sum(p % -mask + 1 for p in range(T))), float(T)
-                return T * (T + 1) / 2.0, float(T)
+                return float(sum(seen(p, mask) for p in range(T))), float(T)
 
             def decode_visible(mask):
-                seen = (context + 1) % -mask + 1 if mask < 0 else context + 2.0
-                return R * float(seen), R * float(seen)
+                return R * float(seen(context + 1, mask)), R * float(seen(context + 1, mask))
 
             prefill_kernels = _kernel_rows(timer.summary(), T, T * (T + 1) / 2.0, T, size, design.split("-")[0], peaks, prefill_visible)
             runner.cache.close(pages)
@@ -458,7 +517,7 @@ def compare_designs(args) -> int:
             with ops.launch_timer() as timer:
                 runner.step([StepEntry(request, prompt(1), [0]) for request in held], check_errors=False)
             decode_kernels = _kernel_rows(timer.summary(), R, R * (context + 2.0), R * (context + 2.0), size, design.split("-")[0], peaks,
-                                          decode_visible)
+                                          decode_visible, requests=R)
             ops.check_device_errors(runner.rt.device)
             out[f"{size_name}/{design}"] = {
                 "prefill_tokens_per_s": T / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
@@ -503,7 +562,7 @@ def main() -> int:
                              "equal layer sizes (--sizes), with every step's time by kernel; a line of its own.")
     parser.add_argument("--sizes", default="2k,4k", help="layer sizes of --workload designs: " + ", ".join(DESIGN_SIZES))
     parser.add_argument("--designs", default="zoferax,qwen3-dense",
-                        help="which designs --workload designs measures, comma separated: zoferax, silupel, qwen3-dense")
+                        help="which designs --workload designs measures, comma separated: zoferax, silupel, figalix, qwen3-dense")
     args = parser.parse_args()
 
     if args.impl == "reference":

@@ -175,15 +175,20 @@ def gated_ffn(n, w, prefix):
     return (silu(n @ w[prefix + "gate"].T) * (n @ w[prefix + "up"].T)) @ w[prefix + "down"].T
 
 
-def router_choice(n, w, mlp, prefix):
-    """(chosen ids [T, top], their weights [T, top]): the largest of softmax over ALL experts, weights as they are."""
-    scores = torch.softmax(n @ w[prefix + "router"].T, dim=-1)
-    weights, ids = torch.topk(scores, mlp["router"]["top"], dim=-1)
+def router_choice(n, w, mlp, prefix, margins=None):
+    """(chosen ids [T, top], their weights [T, top]): the largest of softmax over ALL experts, weights as they are.
+    ``margins`` (a list) receives [T]: how far the last chosen logit lies above the first one left out."""
+    logits = n @ w[prefix + "router"].T
+    top = mlp["router"]["top"]
+    weights, ids = torch.topk(torch.softmax(logits, dim=-1), top, dim=-1)
+    if margins is not None:
+        ranked = logits.sort(dim=-1, descending=True).values
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < logits.shape[1] else torch.full((n.shape[0],), math.inf, dtype=F))
     return ids, weights
 
 
-def routed_ffn(n, w, mlp, prefix):
-    ids, weights = router_choice(n, w, mlp, prefix)
+def routed_ffn(n, w, mlp, prefix, margins=None):
+    ids, weights = router_choice(n, w, mlp, prefix, margins)
     out = torch.zeros(n.shape[0], w[prefix + "e0.down"].shape[0], dtype=F)
     for t in range(n.shape[0]):
         for e, g in zip(ids[t].tolist(), weights[t]):
@@ -194,8 +199,11 @@ def routed_ffn(n, w, mlp, prefix):
 
 
 # ---- the model ----------------------------------------------------------------------------------------------------------
-def forward(c, w, tokens, return_layers=False):
-    """Logits [T, vocab] of a whole sequence (and the stream after every layer)."""
+def forward(c, w, tokens, return_layers=False, margins=None, round_inputs=False):
+    """Logits [T, vocab] of a whole sequence (and the stream after every layer).  ``margins`` (a list) receives one
+    [T] tensor per layer with routed experts, see ``router_choice``.  ``round_inputs`` rounds the rows that every
+    sub-layer reads to bfloat16 and nothing else: how far the logits move then says which positions are sensitive to
+    rounding at all."""
     w = {name: (t.to(F) if t.is_floating_point() else t) for name, t in w.items()}
     eps, mult = c["norm"]["eps"], c["residual_mult"]
     x = w["embed"][torch.tensor(tokens)]
@@ -203,6 +211,8 @@ def forward(c, w, tokens, return_layers=False):
     for i, layer in enumerate(c["layers"]):
         base = f"l{i}."
         n = dynamic_tanh(x, w, base + "norm1")
+        if round_inputs:
+            n = n.to(torch.bfloat16).to(F)
         if layer["type"] == "parallel":
             x = x + mult * parallel_mixer(n, w, layer["mixer"], base + "mix.", eps)
         elif layer["type"] == "mamba2":
@@ -212,10 +222,12 @@ def forward(c, w, tokens, return_layers=False):
         mlp = layer.get("mlp")
         if mlp is not None:
             n = dynamic_tanh(x, w, base + "norm2")
+            if round_inputs:
+                n = n.to(torch.bfloat16).to(F)
             if mlp["kind"] == "dense":
                 x = x + mult * gated_ffn(n, w, base + "mlp.")
             else:
-                x = x + mult * routed_ffn(n, w, mlp, base + "mlp.")
+                x = x + mult * routed_ffn(n, w, mlp, base + "mlp.", margins)
         streams.append(x)
     logits = dynamic_tanh(x, w, "final.norm") @ w["embed"].T
     cap = c.get("logit_softcap")
