@@ -374,6 +374,17 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
                 cols = (width // 256) * (2 * FIGALIX_MEMORY["dim"] + 2 * FIGALIX_MEMORY["vdim"] + 2)
             simt = 6.0 * tokens * cells * count
             bytes_ = (4.0 * tokens * cols + 8.0 * cells * requests) * count
+        elif "ssm_chunks" in name or "matrix_memory_chunks" in name:
+            # chunks of 64 tokens: a token meets the chunk's earlier tokens (scores over the state's rows, weighted values) and
+            # the carried state twice (read-out, the chunk's share of the update), in 32-bit on the ordinary pipe
+            if "ssm" in name:
+                s_heads, s_d, s_dv = 2 * width // FIGALIX_STATE["vdim"], FIGALIX_STATE["state"], FIGALIX_STATE["vdim"]
+                cols = 2 * width + 2 * FIGALIX_STATE["state"] + 2 * width // FIGALIX_STATE["vdim"] + 2 * width
+            else:
+                s_heads, s_d, s_dv = width // 256, FIGALIX_MEMORY["dim"], FIGALIX_MEMORY["vdim"]
+                cols = (width // 256) * (2 * FIGALIX_MEMORY["dim"] + 2 * FIGALIX_MEMORY["vdim"] + 2)
+            simt = tokens * s_heads * (64.0 * (s_d + s_dv) + 4.0 * s_d * s_dv) * count
+            bytes_ = (4.0 * tokens * cols + 8.0 * s_heads * s_d * s_dv * requests) * count
         elif "conv_silu" in name:
             bytes_ = tokens * (2 * width + 2 * FIGALIX_STATE["state"]) * 8.0 * count
         elif "gated_group_norm" in name:

@@ -26,6 +26,7 @@ SOURCES = [
     "layer_forms.cu",
     "mixer_forms.cu",
     "state_forms.cu",
+    "state_chunks.cu",
     "experts.cu",
     "gemm_simt.cu",
     "attention_plain.cu",
@@ -36,7 +37,7 @@ SOURCES = [
     "attention_tcgen05.cu",
     "wait_selftest.cu",
 ]
-HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "no_alloc.h"]
+HEADERS = ["common.cuh", "state_math.cuh", "sm100.cuh", "tensor_map.cuh", "no_alloc.h"]
 
 NVCC_FLAGS = [
     "-gencode",

@@ -594,13 +594,27 @@ def conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor],
     return out
 
 
+STATE_WALK_LIMIT = 8  # steps whose longest run of tokens is at most this walk a matrix state token by token
+
+
+def _state_chunked(batch, state_rows: int, walk_limit: Optional[int]) -> bool:
+    """Whether this step's runs go through a matrix state in chunks: some run is longer than the walk's limit, and a
+    head of ``state_rows`` rows fits the chunked kernels' shared memory."""
+    if batch.max_query_len <= (STATE_WALK_LIMIT if walk_limit is None else walk_limit):
+        return False
+    fn = library().kirai_state_chunks_fit
+    fn.restype = ctypes.c_int
+    return bool(fn(ctypes.c_int(state_rows)))
+
+
 def ssm_walk(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor,
-             state: torch.Tensor, ssm_offset: int, batch, heads: int, groups: int, state_size: int, head_dim: int) -> torch.Tensor:
+             state: torch.Tensor, ssm_offset: int, batch, heads: int, groups: int, state_size: int, head_dim: int,
+             walk_limit: Optional[int] = None) -> torch.Tensor:
     """The state-space recurrence over each request's tokens of this step.  ``xbc`` [T, H P + 2 G N] (float32): x, B
     and C; ``dt`` [T, H] (float32, a run of columns of a wider tensor is allowed): step sizes before softplus.  Per
     head h (group h // (H / G)): dt = softplus(dt + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C +
     skip x, S [N, P] in the request's slot of ``state`` [slots, L] from column ``ssm_offset``.  Returns y [T, H P]
-    (float32)."""
+    (float32).  A step whose longest run of tokens is above ``walk_limit`` takes the runs a chunk of tokens at a time."""
     _need_cuda(xbc, dt, dt_bias, a_log, skip, state)
     inner = heads * head_dim
     assert xbc.dtype == torch.float32 and xbc.is_contiguous() and xbc.shape[1] == inner + 2 * groups * state_size
@@ -609,20 +623,23 @@ def ssm_walk(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
         assert t.dtype == torch.float32 and t.numel() == heads and t.is_contiguous()
     assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
     y = torch.empty((xbc.shape[0], inner), dtype=torch.float32, device=xbc.device)
-    _call("kirai_ssm_walk", _ptr(xbc), _ptr(dt), _l(dt.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state),
+    chunked = _state_chunked(batch, state_size, walk_limit)
+    _call("kirai_ssm_chunks" if chunked else "kirai_ssm_walk", _ptr(xbc), _ptr(dt), _l(dt.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state),
           _l(state.shape[1]), _l(ssm_offset), _ptr(batch.query_start), _ptr(batch.slots), _ptr(y), _i(batch.num_requests),
           _i(heads), _i(groups), _i(state_size), _i(head_dim), _i(state.shape[0]), _stream())
     return y
 
 
 def matrix_memory_walk(rows: torch.Tensor, in_bias: Optional[torch.Tensor], keep_bias: Optional[torch.Tensor], cap: float,
-                       q_scale: float, state: torch.Tensor, batch, heads: int, key_dim: int, value_dim: int) -> torch.Tensor:
+                       q_scale: float, state: torch.Tensor, batch, heads: int, key_dim: int, value_dim: int,
+                       walk_limit: Optional[int] = None) -> torch.Tensor:
     """The matrix memory with exponential gates over each request's tokens of this step.  ``rows`` (float32; further
     columns are left alone): q [H d], k [H d], v [H dv], the input gates' [H] and the forget gates' [H]
     pre-activations.  log_in = cap tanh((. + in_bias) / cap), log_keep = logsigmoid(cap tanh((. + keep_bias) / cap)),
     m' = max(log_keep + m, log_in), S <- exp(log_keep + m - m') S + exp(log_in - m') k v^T, n likewise with k alone,
     o = S^T (q q_scale) / (max(|n . q q_scale|, exp(-m')) + 1e-6).  The request's slot of ``state`` [slots, L] holds
-    S [H, d, dv], n [H, d], m [H].  Returns o [T, H dv] (float32)."""
+    S [H, d, dv], n [H, d], m [H].  Returns o [T, H dv] (float32).  A step whose longest run of tokens is above
+    ``walk_limit`` takes the runs a chunk of tokens at a time."""
     _need_cuda(rows, in_bias, keep_bias, state)
     assert rows.dtype == torch.float32 and rows.dim() == 2 and rows.stride(1) == 1
     assert rows.shape[1] >= heads * (2 * key_dim + value_dim + 2)
@@ -630,6 +647,12 @@ def matrix_memory_walk(rows: torch.Tensor, in_bias: Optional[torch.Tensor], keep
         assert t is None or (t.dtype == torch.float32 and t.numel() == heads and t.is_contiguous())
     assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
     o = torch.empty((rows.shape[0], heads * value_dim), dtype=torch.float32, device=rows.device)
+    if _state_chunked(batch, key_dim, walk_limit):
+        tail = torch.empty((batch.num_requests, heads, key_dim + 1), dtype=torch.float32, device=rows.device)
+        _call("kirai_matrix_memory_chunks", _ptr(rows), _l(rows.stride(0)), _ptr(in_bias), _ptr(keep_bias), _f(cap), _f(q_scale),
+              _ptr(state), _l(state.shape[1]), _ptr(batch.query_start), _ptr(batch.slots), _ptr(o), _ptr(tail),
+              _i(batch.num_requests), _i(heads), _i(key_dim), _i(value_dim), _i(state.shape[0]), _stream())
+        return o
     _call("kirai_matrix_memory_walk", _ptr(rows), _l(rows.stride(0)), _ptr(in_bias), _ptr(keep_bias), _f(cap), _f(q_scale),
           _ptr(state), _l(state.shape[1]), _ptr(batch.query_start), _ptr(batch.slots), _ptr(o), _i(batch.num_requests), _i(heads),
           _i(key_dim), _i(value_dim), _i(state.shape[0]), _stream())

@@ -18,14 +18,7 @@
 // of a block holds rows s, s + SPLIT, ... of column p, and the SPLIT threads of a column sit side by side in a warp,
 // so the sums over the state's rows are shuffles and a token costs no block-wide barrier.
 #include "common.cuh"
-
-__device__ __forceinline__ float sf_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
-__device__ __forceinline__ float sf_silu(float x) { return x * sf_sigmoid(x); }
-__device__ __forceinline__ float sf_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
-__device__ __forceinline__ float sf_log_sigmoid(float x) { return -sf_softplus(-x); }
-__device__ __forceinline__ float sf_gelu_tanh(float z) {
-    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-}
+#include "state_math.cuh"
 
 // ------------------------------------------------------------------ add + Dynamic Tanh
 // One block per produced row.  Without row_index: resid[row] += factor * (d1[row] + d2[row]) (either may be null) and
@@ -119,17 +112,20 @@ KIRAI_EXPORT int kirai_rms_pair_mean(const float* a, const float* b, const float
 }
 
 // ------------------------------------------------------- gate and unit-RMS norm over groups
-// A warp per (row, group).  y [T, width] (float32, row stride y_stride), gate (float32, row stride g_stride),
-// weight [width].  mode 0: v = y * silu(gate), out = v / rms_group(v) * weight (the gate comes before the norm);
-// mode 1: out = y / rms_group(y) * weight * sigmoid(gate) (the gate comes after it).
-template <typename O>
+// A warp per (row, group), or a block where a group is wide.  y [T, width] (float32, row stride y_stride), gate
+// (float32, row stride g_stride), weight [width].  mode 0: v = y * silu(gate), out = v / rms_group(v) * weight (the gate
+// comes before the norm); mode 1: out = y / rms_group(y) * weight * sigmoid(gate) (the gate comes after it).
+template <typename O, int WARPS>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, long y_stride, const float* __restrict__ gate, long g_stride,
                                         const float* __restrict__ weight, float eps, O* __restrict__ out, long rows, int groups,
                                         int group_width, int mode) {
+    __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const long unit = blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5);
+    // WARPS == 1: eight units a block, a warp each; else one unit a block
+    const int lane = WARPS == 1 ? (threadIdx.x & 31) : threadIdx.x;
+    const int step = WARPS * 32;
+    const long unit = WARPS == 1 ? blockIdx.x * (long)(blockDim.x >> 5) + (threadIdx.x >> 5) : blockIdx.x;
     if (unit >= rows * groups) return;
     const long row = unit / groups;
     const int group = (int)(unit - row * groups);
@@ -137,14 +133,14 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, long y_stri
     const float* py = y + row * y_stride + c0;
     const float* pg = gate + row * g_stride + c0;
     float sum = 0.0f;
-    for (int c = lane; c < group_width; c += 32) {
+    for (int c = lane; c < group_width; c += step) {
         const float v = mode == 0 ? py[c] * sf_silu(pg[c]) : py[c];
         sum = fmaf(v, v, sum);
     }
-    sum = warp_sum(sum);
+    sum = WARPS == 1 ? warp_sum(sum) : block_sum(sum, scratch);
     const float r = rsqrtf(sum / (float)group_width + eps);
     O* po = out + row * (long)groups * group_width + c0;
-    for (int c = lane; c < group_width; c += 32) {
+    for (int c = lane; c < group_width; c += step) {
         const float v = mode == 0 ? py[c] * sf_silu(pg[c]) : py[c] * sf_sigmoid(pg[c]);
         po[c] = from_f32<O>(v * r * weight[c0 + c]);
     }
@@ -156,7 +152,10 @@ static int gated_group_norm_launch(const float* y, long y_stride, const float* g
     if (rows <= 0) return 0;
     if (groups <= 0 || group_width <= 0 || mode < 0 || mode > 1) return KIRAI_ERR_BAD_SIZE;
     const long units = (long)rows * groups;
-    return launch_pdl(gated_group_norm_kernel<O>, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, stream, 1u, y, y_stride, gate,
+    if (group_width >= 512)
+        return launch_pdl(gated_group_norm_kernel<O, 8>, dim3((unsigned)units), dim3(256), 0, stream, 1u, y, y_stride, gate, g_stride,
+                          weight, eps, (O*)out, (long)rows, groups, group_width, mode);
+    return launch_pdl(gated_group_norm_kernel<O, 1>, dim3((unsigned)((units + 7) / 8)), dim3(256), 0, stream, 1u, y, y_stride, gate,
                       g_stride, weight, eps, (O*)out, (long)rows, groups, group_width, mode);
 }
 
@@ -172,7 +171,7 @@ KIRAI_EXPORT int kirai_gated_group_norm_bf16(const float* y, long y_stride, cons
 }
 
 // -------------------------------------------------------------- causal convolution + silu
-// One block per token.  in [T, channels] (float32, row stride in_stride): what the convolution reads; taps_w
+// Blocks (token, run of channels).  in [T, channels] (float32, row stride in_stride): what the convolution reads; taps_w
 // [channels, taps], whose last column weighs the token itself; the rows before a request's first row of this step are
 // the request's `taps - 1` kept rows, state [slots, state_len] from column conv_off, [taps - 1, channels], the newest
 // last (zeros at a sequence's start).  out [T, channels] (float32) = silu(bias + sum_j w[c, j] * in[t - (taps - 1) + j, c]).
@@ -189,7 +188,7 @@ __global__ void conv_silu_kernel(const float* __restrict__ in, long in_stride, c
     if (slot < 0 || slot >= num_slots) return;
     const int local = (int)(token - first);
     const float* kept = state + slot * state_len + conv_off;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         float acc = bias ? bias[c] : 0.0f;
         for (int j = 0; j < taps; ++j) {
             const int at = local - (taps - 1) + j;
@@ -229,7 +228,10 @@ KIRAI_EXPORT int kirai_conv_silu(const float* in, long in_stride, const float* t
     if (channels <= 0 || taps <= 0 || requests <= 0 || conv_off < 0 || conv_off + (long)(taps - 1) * channels > state_len)
         return KIRAI_ERR_BAD_SIZE;
     const int threads = channels >= 1024 ? 256 : 128;
-    int status = launch_pdl(conv_silu_kernel, dim3(tokens), dim3(threads), 0, stream, 1u, in, in_stride, taps_w, bias,
+    // few tokens: a token's channels spread over several blocks, so that a step of single tokens fills more of the device
+    int spread = 1;
+    while (spread < 16 && tokens * spread < 256 && threads * spread * 2 <= channels) spread *= 2;
+    int status = launch_pdl(conv_silu_kernel, dim3(tokens, spread), dim3(threads), 0, stream, 1u, in, in_stride, taps_w, bias,
                             (const float*)state, state_len, conv_off, request_of_token, query_start, slots, out, channels, taps,
                             num_slots);
     if (status != 0 || taps == 1) return status;

@@ -421,6 +421,134 @@ def test_matrix_memory_first_tokens_and_long_decoding(dtype):
         close(dtype, _run_part(part, session, x, cuts), expected, f"cut as {cuts[:3]}...")
 
 
+def _plain_scan(q, k, v, keep_log, take_log, take_scale, S, n, m, floor):
+    """One head's recurrence over rows, in 64-bit and token by token.  ``floor``: the read-out is divided by
+    max(|n . q|, exp(-m)) + 1e-6 and a running maximum is kept (the matrix memory); else neither (the state space)."""
+    out = []
+    for t in range(q.shape[0]):
+        if floor:
+            m_new = max(keep_log[t] + m, take_log[t])
+            keep, take = np.exp(keep_log[t] + m - m_new), np.exp(take_log[t] - m_new)
+            m = m_new
+        else:
+            keep, take = np.exp(keep_log[t]), take_scale[t]
+        S = keep * S + take * np.outer(k[t], v[t])
+        n = keep * n + take * k[t]
+        o = S.T @ q[t]
+        out.append(o / (max(abs(float(n @ q[t])), np.exp(-m)) + 1e-6) if floor else o)
+    return np.stack(out), S, n, m
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,groups,state,vdim", [(4, 2, 16, 8), (3, 3, 40, 20), (2, 1, 128, 64), (2, 1, 256, 80), (1, 1, 5, 3)])
+def test_state_space_runs_in_chunks_as_token_by_token(heads, groups, state, vdim):
+    """Unequal requests in one step (a run shorter than a chunk, one of a chunk exactly, one of a chunk and a token,
+    one of several chunks, a single token) from states that are not zero: the chunked kernel, the walk and a plain
+    loop agree on the outputs and on the states they leave."""
+    from part_helpers import Session
+    from kirai_b200.parts.base import StateNeed
+    from kirai_b200.csrc import ops
+
+    gen = torch.Generator().manual_seed(heads * 100 + state)
+    lens = [9, 64, 65, 200, 1, 33]
+    offset = 7  # the state's columns start behind others
+    L = offset + heads * state * vdim
+    session = Session([StateNeed((L,), torch.float32)], torch.float32, page_size=4, num_pages=4, num_slots=8)
+    batch = session.batch([(f"r{i}", n) for i, n in enumerate(lens)])
+    T, inner = sum(lens), heads * vdim
+    xbc = torch.randn((T, inner + 2 * groups * state), generator=gen)
+    dt = torch.randn((T, heads + 3), generator=gen)[:, 3:]  # a run of columns of a wider tensor
+    dt_bias, a_log, skip = torch.randn(heads, generator=gen), torch.randn(heads, generator=gen) * 1.5, torch.randn(heads, generator=gen)
+    state0 = torch.randn((8, L), generator=gen)
+    results = []
+    for limit in (None, 10 ** 9):
+        st = state0.clone().cuda()
+        y = ops.ssm_walk(xbc.cuda(), dt.cuda(), dt_bias.cuda(), a_log.cuda(), skip.cuda(), st, offset, batch, heads, groups, state, vdim,
+                         walk_limit=limit)
+        results.append((y.cpu(), st.cpu()))
+    (y_c, st_c), (y_w, st_w) = results
+    assert torch.equal(st_c[:, :offset], state0[:, :offset])
+    step = np.log1p(np.exp((dt + dt_bias).double().numpy()))
+    starts = batch.query_start.cpu().tolist()  # (the batch orders its requests itself)
+    assert sorted(b - a for a, b in zip(starts, starts[1:])) == sorted(lens)
+    for r, (first, n) in enumerate(zip(starts, np.diff(starts))):
+        slot = int(batch.slots[r])
+        for h in range(heads):
+            g = h // (heads // groups)
+            rows = slice(first, first + n)
+            q = xbc[rows, inner + groups * state + g * state : inner + groups * state + (g + 1) * state].double().numpy()
+            k = xbc[rows, inner + g * state : inner + (g + 1) * state].double().numpy()
+            v = xbc[rows, h * vdim : (h + 1) * vdim].double().numpy()
+            S0 = state0[slot, offset + h * state * vdim : offset + (h + 1) * state * vdim].double().numpy().reshape(state, vdim)
+            keep_log = -np.exp(float(a_log[h])) * step[rows, h]
+            o, S, _, _ = _plain_scan(q, k, v, keep_log, None, step[rows, h], S0, np.zeros(state), 0.0, False)
+            o = o + float(skip[h]) * v
+            for name, y, st in (("chunks", y_c, st_c), ("walk", y_w, st_w)):
+                got = y[rows, h * vdim : (h + 1) * vdim].double().numpy()
+                assert np.abs(got - o).max() <= 3e-5 * max(1.0, np.abs(o).max()), (name, r, h)
+                got = st[slot, offset + h * state * vdim : offset + (h + 1) * state * vdim].double().numpy().reshape(state, vdim)
+                assert np.abs(got - S).max() <= 3e-5 * max(1.0, np.abs(S).max()), (name, "state", r, h)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("heads,dim,vdim,cap", [(2, 8, 16, 5.0), (3, 40, 20, 15.0), (2, 128, 64, 8.0), (1, 256, 80, 2.0), (1, 3, 5, 10.0)])
+def test_matrix_memory_runs_in_chunks_as_token_by_token(heads, dim, vdim, cap):
+    """The same for the matrix memory, with gates that reach their cap on both sides and carried maxima on both sides
+    of zero, so that within a chunk the running maximum is first the carried one and then a token's."""
+    from part_helpers import Session
+    from kirai_b200.parts.base import StateNeed
+    from kirai_b200.csrc import ops
+
+    gen = torch.Generator().manual_seed(heads * 100 + dim)
+    lens = [9, 64, 65, 200, 1, 33]
+    L = heads * (dim * vdim + dim + 1)
+    session = Session([StateNeed((L,), torch.float32)], torch.float32, page_size=4, num_pages=4, num_slots=8)
+    batch = session.batch([(f"r{i}", n) for i, n in enumerate(lens)])
+    T = sum(lens)
+    width = heads * (2 * dim + vdim + 2)
+    rows_all = torch.randn((T, width + 5), generator=gen)  # further columns are left alone
+    rows_all[:, width - 2 * heads : width] *= 6.0
+    in_bias, keep_bias = torch.randn(heads, generator=gen), torch.randn(heads, generator=gen) + 2.0
+    state0 = torch.randn((8, L), generator=gen)
+    state0[:, heads * (dim * vdim + dim):] *= 4.0  # the carried maxima
+    scale = dim ** -0.5
+    results = []
+    for limit in (None, 10 ** 9):
+        st = state0.clone().cuda()
+        o = ops.matrix_memory_walk(rows_all.cuda(), in_bias.cuda(), keep_bias.cuda(), cap, scale, st, batch, heads, dim, vdim, walk_limit=limit)
+        results.append((o.cpu(), st.cpu()))
+    (o_c, st_c), (o_w, st_w) = results
+    R = rows_all.double().numpy()
+    starts = batch.query_start.cpu().tolist()
+    assert sorted(b - a for a, b in zip(starts, starts[1:])) == sorted(lens)
+    for r, (first, n) in enumerate(zip(starts, np.diff(starts))):
+        slot = int(batch.slots[r])
+        base = state0[slot].double().numpy()
+        for h in range(heads):
+            rows = slice(first, first + n)
+            q = R[rows, h * dim : (h + 1) * dim] * scale
+            k = R[rows, heads * dim + h * dim : heads * dim + (h + 1) * dim]
+            v = R[rows, 2 * heads * dim + h * vdim : 2 * heads * dim + (h + 1) * vdim]
+            gi = R[rows, heads * (2 * dim + vdim) + h] + float(in_bias[h])
+            gf = R[rows, heads * (2 * dim + vdim) + heads + h] + float(keep_bias[h])
+            take_log = cap * np.tanh(gi / cap)
+            capped = cap * np.tanh(gf / cap)
+            keep_log = -np.log1p(np.exp(-capped))
+            S0 = base[h * dim * vdim : (h + 1) * dim * vdim].reshape(dim, vdim)
+            n0 = base[heads * dim * vdim + h * dim : heads * dim * vdim + (h + 1) * dim]
+            m0 = float(base[heads * (dim * vdim + dim) + h])
+            o, S, nn, m = _plain_scan(q, k, v, keep_log, take_log, None, S0, n0, m0, True)
+            for name, got_o, st in (("chunks", o_c, st_c), ("walk", o_w, st_w)):
+                got = got_o[rows, h * vdim : (h + 1) * vdim].double().numpy()
+                # (the read-out divides by |n . q|, a sum whose terms cancel: its 32-bit rounding shows in the quotient)
+                assert np.abs(got - o).max() <= 3e-4 * max(1.0, np.abs(o).max()), (name, r, h)
+                s = st[slot].double().numpy()
+                for what, mine, plain_one in (("S", s[h * dim * vdim : (h + 1) * dim * vdim].reshape(dim, vdim), S),
+                                              ("n", s[heads * dim * vdim + h * dim : heads * dim * vdim + (h + 1) * dim], nn),
+                                              ("m", s[heads * (dim * vdim + dim) + h], m)):
+                    assert np.abs(mine - plain_one).max() <= 1e-4 * max(1.0, np.abs(plain_one).max()), (name, what, r, h)
+
+
 # ---- the window that keeps a sequence's first keys -------------------------------------------------------------------
 ATTENTION_CASES = [  # (heads, kv heads, dim, vdim, scale, rotation, window, kept first keys), width, page size
     (attn(4, 2, 16, 16, 0.7, rot(500.0, 8, (4.0, 32, 4.0, 1.0)), 8, 3), 64, 4),
