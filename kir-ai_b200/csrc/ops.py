@@ -595,6 +595,8 @@ def conv_silu(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor],
 
 
 STATE_WALK_LIMIT = 8  # steps whose longest run of tokens is at most this walk a matrix state token by token
+STATE_CHAIN_LIMIT = 256  # steps with a longer run take their chunks side by side (a carry between them) instead of in a chain
+STATE_SIDE_BYTES = 1 << 30  # ... unless the states at the chunks' starts would take more than this
 
 
 def _state_chunked(batch, state_rows: int, walk_limit: Optional[int]) -> bool:
@@ -607,9 +609,23 @@ def _state_chunked(batch, state_rows: int, walk_limit: Optional[int]) -> bool:
     return bool(fn(ctypes.c_int(state_rows)))
 
 
+def _state_side(batch, tokens: int, heads: int, rows: int, cols: int, normaliser: bool, device, chain_limit: Optional[int]):
+    """(units, state, normaliser, marks): the buffers of a step whose chunks run side by side, or (0, None, None, None)."""
+    fn = library().kirai_state_chunk_tokens
+    fn.restype = ctypes.c_int
+    units = tokens // int(fn()) + batch.num_requests
+    limit = STATE_CHAIN_LIMIT if chain_limit is None else chain_limit
+    if batch.max_query_len <= limit or units * heads * rows * cols * 4 > STATE_SIDE_BYTES:
+        return 0, None, None, None
+    state = torch.empty((units, heads, rows, cols), dtype=torch.float32, device=device)
+    norm = torch.empty((units, heads, rows), dtype=torch.float32, device=device) if normaliser else None
+    marks = torch.empty((units, heads, 3), dtype=torch.float32, device=device)
+    return units, state, norm, marks
+
+
 def ssm_walk(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, skip: torch.Tensor,
              state: torch.Tensor, ssm_offset: int, batch, heads: int, groups: int, state_size: int, head_dim: int,
-             walk_limit: Optional[int] = None) -> torch.Tensor:
+             walk_limit: Optional[int] = None, chain_limit: Optional[int] = None) -> torch.Tensor:
     """The state-space recurrence over each request's tokens of this step.  ``xbc`` [T, H P + 2 G N] (float32): x, B
     and C; ``dt`` [T, H] (float32, a run of columns of a wider tensor is allowed): step sizes before softplus.  Per
     head h (group h // (H / G)): dt = softplus(dt + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C +
@@ -623,8 +639,13 @@ def ssm_walk(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
         assert t.dtype == torch.float32 and t.numel() == heads and t.is_contiguous()
     assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
     y = torch.empty((xbc.shape[0], inner), dtype=torch.float32, device=xbc.device)
-    chunked = _state_chunked(batch, state_size, walk_limit)
-    _call("kirai_ssm_chunks" if chunked else "kirai_ssm_walk", _ptr(xbc), _ptr(dt), _l(dt.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state),
+    if _state_chunked(batch, state_size, walk_limit):
+        units, side, _, marks = _state_side(batch, xbc.shape[0], heads, state_size, head_dim, False, xbc.device, chain_limit)
+        _call("kirai_ssm_chunks", _ptr(xbc), _ptr(dt), _l(dt.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state),
+              _l(state.shape[1]), _l(ssm_offset), _ptr(batch.query_start), _ptr(batch.slots), _ptr(y), _i(batch.num_requests),
+              _i(heads), _i(groups), _i(state_size), _i(head_dim), _i(state.shape[0]), _i(units), _ptr(side), _ptr(marks), _stream())
+        return y
+    _call("kirai_ssm_walk", _ptr(xbc), _ptr(dt), _l(dt.stride(0)), _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(state),
           _l(state.shape[1]), _l(ssm_offset), _ptr(batch.query_start), _ptr(batch.slots), _ptr(y), _i(batch.num_requests),
           _i(heads), _i(groups), _i(state_size), _i(head_dim), _i(state.shape[0]), _stream())
     return y
@@ -632,7 +653,7 @@ def ssm_walk(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
 
 def matrix_memory_walk(rows: torch.Tensor, in_bias: Optional[torch.Tensor], keep_bias: Optional[torch.Tensor], cap: float,
                        q_scale: float, state: torch.Tensor, batch, heads: int, key_dim: int, value_dim: int,
-                       walk_limit: Optional[int] = None) -> torch.Tensor:
+                       walk_limit: Optional[int] = None, chain_limit: Optional[int] = None) -> torch.Tensor:
     """The matrix memory with exponential gates over each request's tokens of this step.  ``rows`` (float32; further
     columns are left alone): q [H d], k [H d], v [H dv], the input gates' [H] and the forget gates' [H]
     pre-activations.  log_in = cap tanh((. + in_bias) / cap), log_keep = logsigmoid(cap tanh((. + keep_bias) / cap)),
@@ -648,10 +669,12 @@ def matrix_memory_walk(rows: torch.Tensor, in_bias: Optional[torch.Tensor], keep
     assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
     o = torch.empty((rows.shape[0], heads * value_dim), dtype=torch.float32, device=rows.device)
     if _state_chunked(batch, key_dim, walk_limit):
-        tail = torch.empty((batch.num_requests, heads, key_dim + 1), dtype=torch.float32, device=rows.device)
+        units, side, norm, marks = _state_side(batch, rows.shape[0], heads, key_dim, value_dim, True, rows.device, chain_limit)
+        tail = None if units else torch.empty((batch.num_requests, heads, key_dim + 1), dtype=torch.float32, device=rows.device)
         _call("kirai_matrix_memory_chunks", _ptr(rows), _l(rows.stride(0)), _ptr(in_bias), _ptr(keep_bias), _f(cap), _f(q_scale),
               _ptr(state), _l(state.shape[1]), _ptr(batch.query_start), _ptr(batch.slots), _ptr(o), _ptr(tail),
-              _i(batch.num_requests), _i(heads), _i(key_dim), _i(value_dim), _i(state.shape[0]), _stream())
+              _i(batch.num_requests), _i(heads), _i(key_dim), _i(value_dim), _i(state.shape[0]), _i(units), _ptr(side), _ptr(norm),
+              _ptr(marks), _stream())
         return o
     _call("kirai_matrix_memory_walk", _ptr(rows), _l(rows.stride(0)), _ptr(in_bias), _ptr(keep_bias), _f(cap), _f(q_scale),
           _ptr(state), _l(state.shape[1]), _ptr(batch.query_start), _ptr(batch.slots), _ptr(o), _i(batch.num_requests), _i(heads),

@@ -421,6 +421,11 @@ def test_matrix_memory_first_tokens_and_long_decoding(dtype):
         close(dtype, _run_part(part, session, x, cuts), expected, f"cut as {cuts[:3]}...")
 
 
+# the three forms of a step's runs through a matrix state: chunks one after another in a block, chunks side by side with
+# a carry between them, and token by token
+FORMS = (dict(chain_limit=10 ** 9), dict(chain_limit=0), dict(walk_limit=10 ** 9))
+
+
 def _plain_scan(q, k, v, keep_log, take_log, take_scale, S, n, m, floor):
     """One head's recurrence over rows, in 64-bit and token by token.  ``floor``: the read-out is divided by
     max(|n . q|, exp(-m)) + 1e-6 and a running maximum is kept (the matrix memory); else neither (the state space)."""
@@ -443,7 +448,7 @@ def _plain_scan(q, k, v, keep_log, take_log, take_scale, S, n, m, floor):
 @pytest.mark.parametrize("heads,groups,state,vdim", [(4, 2, 16, 8), (3, 3, 40, 20), (2, 1, 128, 64), (2, 1, 256, 80), (1, 1, 5, 3)])
 def test_state_space_runs_in_chunks_as_token_by_token(heads, groups, state, vdim):
     """Unequal requests in one step (a run shorter than a chunk, one of a chunk exactly, one of a chunk and a token,
-    one of several chunks, a single token) from states that are not zero: the chunked kernel, the walk and a plain
+    one of several chunks, a single token) from states that are not zero: the chunked kernels (both forms), the walk and a plain
     loop agree on the outputs and on the states they leave."""
     from part_helpers import Session
     from kirai_b200.parts.base import StateNeed
@@ -461,12 +466,12 @@ def test_state_space_runs_in_chunks_as_token_by_token(heads, groups, state, vdim
     dt_bias, a_log, skip = torch.randn(heads, generator=gen), torch.randn(heads, generator=gen) * 1.5, torch.randn(heads, generator=gen)
     state0 = torch.randn((8, L), generator=gen)
     results = []
-    for limit in (None, 10 ** 9):
+    for limits in FORMS:
         st = state0.clone().cuda()
         y = ops.ssm_walk(xbc.cuda(), dt.cuda(), dt_bias.cuda(), a_log.cuda(), skip.cuda(), st, offset, batch, heads, groups, state, vdim,
-                         walk_limit=limit)
+                         **limits)
         results.append((y.cpu(), st.cpu()))
-    (y_c, st_c), (y_w, st_w) = results
+    (y_c, st_c), (y_s, st_s), (y_w, st_w) = results
     assert torch.equal(st_c[:, :offset], state0[:, :offset])
     step = np.log1p(np.exp((dt + dt_bias).double().numpy()))
     starts = batch.query_start.cpu().tolist()  # (the batch orders its requests itself)
@@ -483,7 +488,7 @@ def test_state_space_runs_in_chunks_as_token_by_token(heads, groups, state, vdim
             keep_log = -np.exp(float(a_log[h])) * step[rows, h]
             o, S, _, _ = _plain_scan(q, k, v, keep_log, None, step[rows, h], S0, np.zeros(state), 0.0, False)
             o = o + float(skip[h]) * v
-            for name, y, st in (("chunks", y_c, st_c), ("walk", y_w, st_w)):
+            for name, y, st in (("chunks in a chain", y_c, st_c), ("chunks side by side", y_s, st_s), ("walk", y_w, st_w)):
                 got = y[rows, h * vdim : (h + 1) * vdim].double().numpy()
                 assert np.abs(got - o).max() <= 3e-5 * max(1.0, np.abs(o).max()), (name, r, h)
                 got = st[slot, offset + h * state * vdim : offset + (h + 1) * state * vdim].double().numpy().reshape(state, vdim)
@@ -513,11 +518,11 @@ def test_matrix_memory_runs_in_chunks_as_token_by_token(heads, dim, vdim, cap):
     state0[:, heads * (dim * vdim + dim):] *= 4.0  # the carried maxima
     scale = dim ** -0.5
     results = []
-    for limit in (None, 10 ** 9):
+    for limits in FORMS:
         st = state0.clone().cuda()
-        o = ops.matrix_memory_walk(rows_all.cuda(), in_bias.cuda(), keep_bias.cuda(), cap, scale, st, batch, heads, dim, vdim, walk_limit=limit)
+        o = ops.matrix_memory_walk(rows_all.cuda(), in_bias.cuda(), keep_bias.cuda(), cap, scale, st, batch, heads, dim, vdim, **limits)
         results.append((o.cpu(), st.cpu()))
-    (o_c, st_c), (o_w, st_w) = results
+    (o_c, st_c), (o_s, st_s), (o_w, st_w) = results
     R = rows_all.double().numpy()
     starts = batch.query_start.cpu().tolist()
     assert sorted(b - a for a, b in zip(starts, starts[1:])) == sorted(lens)
@@ -538,7 +543,7 @@ def test_matrix_memory_runs_in_chunks_as_token_by_token(heads, dim, vdim, cap):
             n0 = base[heads * dim * vdim + h * dim : heads * dim * vdim + (h + 1) * dim]
             m0 = float(base[heads * (dim * vdim + dim) + h])
             o, S, nn, m = _plain_scan(q, k, v, keep_log, take_log, None, S0, n0, m0, True)
-            for name, got_o, st in (("chunks", o_c, st_c), ("walk", o_w, st_w)):
+            for name, got_o, st in (("chunks in a chain", o_c, st_c), ("chunks side by side", o_s, st_s), ("walk", o_w, st_w)):
                 got = got_o[rows, h * vdim : (h + 1) * vdim].double().numpy()
                 # (the read-out divides by |n . q|, a sum whose terms cancel: its 32-bit rounding shows in the quotient)
                 assert np.abs(got - o).max() <= 3e-4 * max(1.0, np.abs(o).max()), (name, r, h)
