@@ -821,6 +821,32 @@ def test_whole_then_last_tokens_one_by_one(tiny, dtype, tmp_path):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_prompt_of_many_chunks_whole_and_in_portions(tiny, dtype, tmp_path):
+    """A prompt long enough for the recurrent mixers to take its chunks side by side, whole and beside a second request;
+    the same prompt in portions that go through the chunks in a chain and through the walk; both against the plain
+    model."""
+    from replay_client import Replay
+
+    toks = random_tokens(330, tiny["raw"]["vocab"], 77)
+    other = tiny["sequences"]["d"]
+    reference = reference_with_close_calls(tiny["config"], tiny["weights"], toks)
+    rows = [0, 1, 63, 64, 65, 127, 128, 200, 255, 256, 257, 300, 328, 329]
+    replay = Replay(tiny["folder"], dtype, str(tmp_path / "out"), max_tokens=512, page_size=tiny["page"])
+    got = replay.step([("long", toks, rows), ("d", other, [len(other) - 1])], end=["long", "d"])
+    check(dtype, got[: len(rows)], reference, rows, "whole, beside a short request")
+    check(dtype, got[len(rows) :], tiny["reference"]["d"], [len(other) - 1], "the short request beside it")
+    done = 0
+    for size in (130, 3, 70, 1, 100, 26):  # chains of three and two chunks, walks, a single token
+        want = [r - done for r in rows if done <= r < done + size]
+        got = replay.step([("again", toks[done : done + size], want)], end=["again"] if done + size == len(toks) else [])
+        if want:
+            check(dtype, got, reference, [r + done for r in want], f"portion at {done}")
+        done += size
+    assert done == len(toks) and replay.close() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_portions_down_to_two_tokens(tiny, dtype, tmp_path):
     """Portions that end inside a page, inside a window, among the kept first keys and inside the convolution's reach."""
     from replay_client import Replay
