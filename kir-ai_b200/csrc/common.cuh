@@ -79,6 +79,14 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return total;
 }
 
+// A gated activation with clamped inputs: g' = min(gate, limit), u' = clamp(up, -limit, limit), and the result is
+// g' * sigmoid(slope * g') * (u' + 1).
+__device__ __forceinline__ float clamped_gated_f32(float gate, float up, float limit, float slope) {
+    const float g = fminf(gate, limit);
+    const float u = fminf(fmaxf(up, -limit), limit);
+    return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+}
+
 // ---- which keys a query sees, and what becomes of a score -------------------
 // `window` > 0: the last `window` keys up to the query's own position; `window` < 0: the keys of the query's own
 // chunk of -window positions (chunks counted from position 0 of the sequence); 0: every key up to its own position.

@@ -3,7 +3,10 @@
 //   router_gates   logits z = W_router x in 32-bit (spread over blocks by expert; the block of a token that finishes last goes on);
 //                  the `top` largest are chosen (the lower index wins a tie) and the
 //                  token's weights are the softmax over the chosen logits alone (or, with `over_all`, the chosen
-//                  experts' shares of the softmax over ALL logits, which then do not sum to one).  The result is the dense matrix
+//                  experts' shares of the softmax over ALL logits, which then do not sum to one; or, with rule 2, sigmoid
+//                  scores: the choice looks at sigmoid(z) + correction, and only inside the `keep` of `groups` equal
+//                  groups of neighbouring experts whose two largest such numbers sum highest, and the weights are
+//                  the chosen experts' sigmoid(z) as they are).  The result is the dense matrix
 //                  gates [T, experts], zero where an expert was not chosen, plus the chosen ids and weights.
 //   relu2_gate     hidden[t, e * ff + j] = relu(up[t, e * ff + j])^2 * gates[t, e]: with the experts' up matrices
 //                  stacked along the rows and their down matrices side by side along the columns, the product
@@ -27,13 +30,60 @@ __device__ __forceinline__ float4 load4(const bf16* p) {
 // What the block that finishes a token's logits last does with them: warp `warp` of `warps` takes the token's row `out`
 // [experts] of logits (read past L1), picks the `top` largest one after the other (the lower index wins a tie) and
 // overwrites the row with the routing weights.  `logits_s` [experts] is this warp's shared scratch.
+// How the weights come from the logits.  mode 0: softmax over the chosen logits; 1: the chosen experts' shares of the
+// softmax over all; 2: sigmoid scores with a correction on the choice and a choice among groups (see the top of the file).
+struct RouterRule {
+    int mode;
+    const float* correction;  // [experts] or null (mode 2)
+    int groups, keep;         // mode 2; one group of which one is kept: no limit
+};
+// Floats of shared scratch a warp needs to choose for one token: logits, scores, group scores.
+#define ROUTER_SCRATCH(experts) (3 * (size_t)(experts))
+
 __device__ __forceinline__ void choose_experts(float* __restrict__ out, float* logits_s, int* __restrict__ chosen_ids,
                                                float* __restrict__ chosen_weights, int experts, int top, int lane,
-                                               int over_all = 0) {
+                                               const RouterRule rule) {
+    const int over_all = rule.mode == 1;
+    const bool scored = rule.mode == 2;
+    float* scores_s = logits_s + experts;       // mode 2: sigmoid(z), the weights
+    float* groups_s = logits_s + 2 * experts;   // mode 2: every group's two largest choice scores, summed
     for (int i = lane; i < experts; i += 32) logits_s[i] = __ldcg(out + i);
     __syncwarp();
     for (int i = lane; i < experts; i += 32) out[i] = 0.0f;
     __syncwarp();
+    if (scored) {
+        for (int i = lane; i < experts; i += 32) {
+            const float score = 1.0f / (1.0f + expf(-logits_s[i]));
+            scores_s[i] = score;
+            logits_s[i] = score + (rule.correction ? rule.correction[i] : 0.0f);  // what the choice looks at
+        }
+        __syncwarp();
+        if (rule.groups > 1 && rule.keep < rule.groups) {
+            const int size = experts / rule.groups;
+            for (int g = lane; g < rule.groups; g += 32) {
+                float first = -INFINITY, second = -INFINITY;
+                for (int j = 0; j < size; ++j) {
+                    const float c = logits_s[g * size + j];
+                    if (c > first) second = first, first = c;
+                    else if (c > second) second = c;
+                }
+                groups_s[g] = size > 1 ? first + second : first;
+            }
+            __syncwarp();
+            // a group stays open when fewer than `keep` groups stand ahead of it (the lower index wins a tie)
+            for (int g = lane; g < rule.groups; g += 32) {
+                const float mine = groups_s[g];
+                int ahead = 0;
+                for (int o = 0; o < rule.groups; ++o) {
+                    const float other = groups_s[o];
+                    ahead += (other > mine || (other == mine && o < g)) ? 1 : 0;
+                }
+                if (ahead >= rule.keep)
+                    for (int j = 0; j < size; ++j) logits_s[g * size + j] = -INFINITY;
+            }
+            __syncwarp();
+        }
+    }
     float best_first = 0.0f, denom = 0.0f, all_sum = 0.0f;
     if (over_all) {
         // the softmax's denominator over every expert, before any logit is struck out
@@ -68,7 +118,7 @@ __device__ __forceinline__ void choose_experts(float* __restrict__ out, float* l
             break;
         }
         if (k == 0) best_first = best;
-        const float weight = expf(best - best_first);  // the first chosen logit is the largest
+        const float weight = scored ? scores_s[best_e] : expf(best - best_first);  // the first chosen logit is the largest
         denom += weight;
         if (lane == 0) {
             out[best_e] = weight;
@@ -79,7 +129,7 @@ __device__ __forceinline__ void choose_experts(float* __restrict__ out, float* l
     }
     __syncwarp();
     if (over_all) denom = all_sum;  // (the first chosen logit is the maximum of all)
-    const float inv = denom > 0.0f ? 1.0f / denom : 0.0f;
+    const float inv = scored ? 1.0f : (denom > 0.0f ? 1.0f / denom : 0.0f);
     for (int i = lane; i < experts; i += 32) out[i] *= inv;
     if (chosen_weights)
         for (int k = lane; k < top; k += 32) chosen_weights[k] *= inv;
@@ -107,7 +157,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_gates_few_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ router, float* __restrict__ gates,
                         int* __restrict__ chosen_ids, float* __restrict__ chosen_weights, int* __restrict__ arrivals, int hidden,
-                        int experts, int top, int over_all) {
+                        int experts, int top, RouterRule rule) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float logits_s[];  // [experts]
@@ -140,7 +190,7 @@ router_gates_few_kernel(const T* __restrict__ x, long x_stride, const float* __r
     if (!arrives_last(&arrivals[token], (int)gridDim.y, &is_last)) return;
     if (warp == 0)
         choose_experts(out, logits_s, chosen_ids ? chosen_ids + (size_t)token * top : nullptr,
-                       chosen_weights ? chosen_weights + (size_t)token * top : nullptr, experts, top, lane, over_all);
+                       chosen_weights ? chosen_weights + (size_t)token * top : nullptr, experts, top, lane, rule);
 }
 
 // Many tokens: a block takes ROUTER_TOKENS tokens and ROUTER_WARPS experts, a warp per expert, so that a router row is
@@ -151,7 +201,7 @@ template <typename T>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_gates_many_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ router, float* __restrict__ gates,
                          int* __restrict__ chosen_ids, float* __restrict__ chosen_weights, int* __restrict__ arrivals, int tokens,
-                         int hidden, int experts, int top, int over_all) {
+                         int hidden, int experts, int top, RouterRule rule) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float logits_s[];  // [ROUTER_WARPS][experts]
@@ -194,63 +244,77 @@ router_gates_many_kernel(const T* __restrict__ x, long x_stride, const float* __
     if (!arrives_last(&arrivals[blockIdx.x], (int)gridDim.y, &is_last)) return;
     for (int t = warp; t < count; t += ROUTER_WARPS) {
         const size_t token = (size_t)(first + t);
-        choose_experts(gates + token * experts, logits_s + (size_t)warp * experts, chosen_ids ? chosen_ids + token * top : nullptr,
-                       chosen_weights ? chosen_weights + token * top : nullptr, experts, top, lane, over_all);
+        choose_experts(gates + token * experts, logits_s + warp * ROUTER_SCRATCH(experts), chosen_ids ? chosen_ids + token * top : nullptr,
+                       chosen_weights ? chosen_weights + token * top : nullptr, experts, top, lane, rule);
     }
+}
+
+// Whether a rule fits the experts it is to choose among.
+static bool router_rule_fits(const RouterRule& rule, int experts, int top) {
+    if (rule.mode < 0 || rule.mode > 2) return false;
+    if (rule.mode != 2) return true;
+    if (rule.groups <= 0 || rule.keep <= 0 || rule.keep > rule.groups || experts % rule.groups != 0) return false;
+    return top <= rule.keep * (experts / rule.groups);
 }
 
 template <typename T>
 static int router_gates_launch(const void* x, long x_stride, const float* router, float* gates, int* chosen_ids,
                                float* chosen_weights, int* arrivals, int tokens, int hidden, int experts, int top,
-                               int over_all, cudaStream_t stream) {
+                               RouterRule rule, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (experts <= 0 || top <= 0 || top > experts || hidden <= 0 || experts > 8192 || !arrivals) return KIRAI_ERR_BAD_SIZE;
+    if (experts <= 0 || top <= 0 || top > experts || hidden <= 0 || experts > 1024 || !arrivals) return KIRAI_ERR_BAD_SIZE;
+    if (!router_rule_fits(rule, experts, top)) return KIRAI_ERR_BAD_SIZE;
     if ((chosen_ids == nullptr) != (chosen_weights == nullptr)) return KIRAI_ERR_BAD_SIZE;
     if (tokens * (long)experts <= 4096 && experts <= 65535) {
-        return launch_pdl(router_gates_few_kernel<T>, dim3(tokens, experts), dim3(ROUTER_WARPS * 32), (size_t)experts * sizeof(float),
-                          stream, 1u, (const T*)x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, hidden, experts, top, over_all);
+        return launch_pdl(router_gates_few_kernel<T>, dim3(tokens, experts), dim3(ROUTER_WARPS * 32), ROUTER_SCRATCH(experts) * sizeof(float),
+                          stream, 1u, (const T*)x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, hidden, experts, top, rule);
     }
     const unsigned slices = (unsigned)((experts + ROUTER_WARPS - 1) / ROUTER_WARPS);
     const unsigned groups = (unsigned)((tokens + ROUTER_TOKENS - 1) / ROUTER_TOKENS);
     return launch_pdl(router_gates_many_kernel<T>, dim3(groups, slices), dim3(ROUTER_WARPS * 32),
-                      (size_t)ROUTER_WARPS * experts * sizeof(float), stream, 1u, (const T*)x, x_stride, router, gates, chosen_ids,
-                      chosen_weights, arrivals, tokens, hidden, experts, top, over_all);
+                      ROUTER_WARPS * ROUTER_SCRATCH(experts) * sizeof(float), stream, 1u, (const T*)x, x_stride, router, gates, chosen_ids,
+                      chosen_weights, arrivals, tokens, hidden, experts, top, rule);
 }
 
 // The choice alone, for logits that a product left in `gates` [tokens, experts]: a warp per token.
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_choose_kernel(float* __restrict__ gates, int* __restrict__ chosen_ids, float* __restrict__ chosen_weights, int tokens,
-                     int experts, int top, int over_all) {
+                     int experts, int top, RouterRule rule) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float logits_s[];  // [ROUTER_WARPS][experts]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t token = (size_t)blockIdx.x * ROUTER_WARPS + warp;
     if (token >= (size_t)tokens) return;
-    choose_experts(gates + token * experts, logits_s + (size_t)warp * experts, chosen_ids ? chosen_ids + token * top : nullptr,
-                   chosen_weights ? chosen_weights + token * top : nullptr, experts, top, lane, over_all);
+    choose_experts(gates + token * experts, logits_s + warp * ROUTER_SCRATCH(experts), chosen_ids ? chosen_ids + token * top : nullptr,
+                   chosen_weights ? chosen_weights + token * top : nullptr, experts, top, lane, rule);
 }
 
 // gates [tokens, experts] holds router logits (32-bit) and receives the routing weights; see router_gates.
+// rule, correction, groups, keep: see RouterRule.
 KIRAI_EXPORT int kirai_router_choose(float* gates, int* chosen_ids, float* chosen_weights, int tokens, int experts, int top,
-                                     int over_all, cudaStream_t stream) {
+                                     int rule, const float* correction, int groups, int keep, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (experts <= 0 || top <= 0 || top > experts || experts > 8192) return KIRAI_ERR_BAD_SIZE;
+    if (experts <= 0 || top <= 0 || top > experts || experts > 1024) return KIRAI_ERR_BAD_SIZE;
     if ((chosen_ids == nullptr) != (chosen_weights == nullptr)) return KIRAI_ERR_BAD_SIZE;
+    const RouterRule how{rule, correction, groups, keep};
+    if (!router_rule_fits(how, experts, top)) return KIRAI_ERR_BAD_SIZE;
     return launch_pdl(router_choose_kernel, dim3((unsigned)((tokens + ROUTER_WARPS - 1) / ROUTER_WARPS)), dim3(ROUTER_WARPS * 32),
-                      (size_t)ROUTER_WARPS * experts * sizeof(float), stream, 1u, gates, chosen_ids, chosen_weights, tokens, experts, top, over_all);
+                      ROUTER_WARPS * ROUTER_SCRATCH(experts) * sizeof(float), stream, 1u, gates, chosen_ids, chosen_weights, tokens, experts, top, how);
 }
 
 // arrivals [tokens]: zero before the first launch; every launch leaves it zero.
 KIRAI_EXPORT int kirai_router_gates_f32(const void* x, long x_stride, const float* router, float* gates, int* chosen_ids,
                                         float* chosen_weights, int* arrivals, int tokens, int hidden, int experts, int top,
-                                        int over_all, cudaStream_t stream) {
-    return router_gates_launch<float>(x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, tokens, hidden, experts, top, over_all, stream);
+                                        int rule, const float* correction, int groups, int keep, cudaStream_t stream) {
+    return router_gates_launch<float>(x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, tokens, hidden, experts, top,
+                                      RouterRule{rule, correction, groups, keep}, stream);
 }
 KIRAI_EXPORT int kirai_router_gates_bf16(const void* x, long x_stride, const float* router, float* gates, int* chosen_ids,
                                          float* chosen_weights, int* arrivals, int tokens, int hidden, int experts, int top,
-                                         int over_all, cudaStream_t stream) {
-    return router_gates_launch<bf16>(x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, tokens, hidden, experts, top, over_all, stream);
+                                         int rule, const float* correction, int groups, int keep, cudaStream_t stream) {
+    return router_gates_launch<bf16>(x, x_stride, router, gates, chosen_ids, chosen_weights, arrivals, tokens, hidden, experts, top,
+                                     RouterRule{rule, correction, groups, keep}, stream);
 }
 
 // activation: 0 = relu(z)^2

@@ -151,6 +151,133 @@ KIRAI_EXPORT int kirai_norm_add(float* resid, const float* y, const float* weigh
     return launch_pdl(norm_add_kernel, dim3(rows), dim3(threads), 0, stream, 1u, resid, y, weight, (bf16*)copy, hidden, eps);
 }
 
+// -------------------------------------- norm on the output, then the next norm
+// One block per produced row.  With a sub-layer's 32-bit output y: the stream takes y / rms(y) * w_add, and the sum
+// leaves under the next norm, sum / rms(sum) * w_next, in the runtime dtype: one pass over the row where the two
+// kernels made three.  With row_index only those rows are produced and the stream is not written (the rows ahead of
+// the logits).  The row is kept in shared memory (32-bit) between the two statistics.
+template <typename T>
+__global__ void norm_add_norm_kernel(float* __restrict__ resid, const float* __restrict__ y, const float* __restrict__ w_add,
+                                     const float* __restrict__ w_next, T* __restrict__ out, const int* __restrict__ row_index,
+                                     int hidden, float eps_add, float eps_next) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float row_s[];  // [hidden]
+    __shared__ float scratch[32];
+    const int row = row_index ? row_index[blockIdx.x] : (int)blockIdx.x;
+    const float* src = y + (size_t)row * hidden;
+    float* stream = resid + (size_t)row * hidden;
+    T* dst = out + (size_t)blockIdx.x * hidden;
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = src[i];
+        row_s[i] = v;
+        acc = fmaf(v, v, acc);
+    }
+    const float var_add = block_sum(acc, scratch) / (float)hidden + eps_add;
+    const float scale_add = var_add == 0.0f ? 0.0f : 1.0f / sqrtf(var_add);
+    acc = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = stream[i] + row_s[i] * scale_add * w_add[i];
+        row_s[i] = v;
+        if (!row_index) stream[i] = v;
+        acc = fmaf(v, v, acc);
+    }
+    const float var_next = block_sum(acc, scratch) / (float)hidden + eps_next;
+    const float scale_next = var_next == 0.0f ? 0.0f : 1.0f / sqrtf(var_next);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>(row_s[i] * scale_next * w_next[i]);
+}
+
+template <typename T>
+static int norm_add_norm_launch(float* resid, const float* y, const float* w_add, const float* w_next, void* out,
+                                const int* row_index, int rows, int hidden, float eps_add, float eps_next, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || hidden > 12 * 1024) return KIRAI_ERR_BAD_SIZE;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    return launch_pdl(norm_add_norm_kernel<T>, dim3(rows), dim3(threads), (size_t)hidden * sizeof(float), stream, 1u, resid, y, w_add,
+                      w_next, (T*)out, row_index, hidden, eps_add, eps_next);
+}
+
+KIRAI_EXPORT int kirai_norm_add_norm_f32(float* resid, const float* y, const float* w_add, const float* w_next, void* out,
+                                         const int* row_index, int rows, int hidden, float eps_add, float eps_next,
+                                         cudaStream_t stream) {
+    return norm_add_norm_launch<float>(resid, y, w_add, w_next, out, row_index, rows, hidden, eps_add, eps_next, stream);
+}
+KIRAI_EXPORT int kirai_norm_add_norm_bf16(float* resid, const float* y, const float* w_add, const float* w_next, void* out,
+                                          const int* row_index, int rows, int hidden, float eps_add, float eps_next,
+                                          cudaStream_t stream) {
+    return norm_add_norm_launch<bf16>(resid, y, w_add, w_next, out, row_index, rows, hidden, eps_add, eps_next, stream);
+}
+
+// ------------------------------------------------- the stream beside other rows
+// One block per row: with y, the stream first takes y / rms(y) * weight (as norm_add); then the row leaves in the
+// runtime dtype at out[row * out_stride ...], a run of columns of a wider buffer (two streams side by side, read by one
+// product).  Without y it is a copy alone; `resid` is then only read.
+template <typename T>
+__global__ void stream_copy_kernel(float* __restrict__ resid, const float* __restrict__ y, const float* __restrict__ weight,
+                                   T* __restrict__ out, long out_stride, int hidden, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int row = blockIdx.x;
+    float* stream = resid + (size_t)row * hidden;
+    T* dst = out + (size_t)row * out_stride;
+    if (!y) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>(stream[i]);
+        return;
+    }
+    const float* src = y + (size_t)row * hidden;
+    float acc = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) acc = fmaf(src[i], src[i], acc);
+    const float variance = block_sum(acc, scratch) / (float)hidden + eps;
+    const float scale = variance == 0.0f ? 0.0f : 1.0f / sqrtf(variance);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = stream[i] + src[i] * scale * weight[i];
+        stream[i] = v;
+        dst[i] = from_f32<T>(v);
+    }
+}
+
+template <typename T>
+static int stream_copy_launch(float* resid, const float* y, const float* weight, void* out, long out_stride, int rows, int hidden,
+                              float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || out_stride < hidden || (y && !weight)) return KIRAI_ERR_BAD_SIZE;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    return launch_pdl(stream_copy_kernel<T>, dim3(rows), dim3(threads), 0, stream, 1u, resid, y, weight, (T*)out, out_stride, hidden, eps);
+}
+
+KIRAI_EXPORT int kirai_stream_copy_f32(float* resid, const float* y, const float* weight, void* out, long out_stride, int rows,
+                                       int hidden, float eps, cudaStream_t stream) {
+    return stream_copy_launch<float>(resid, y, weight, out, out_stride, rows, hidden, eps, stream);
+}
+KIRAI_EXPORT int kirai_stream_copy_bf16(float* resid, const float* y, const float* weight, void* out, long out_stride, int rows,
+                                        int hidden, float eps, cudaStream_t stream) {
+    return stream_copy_launch<bf16>(resid, y, weight, out, out_stride, rows, hidden, eps, stream);
+}
+
+// ------------------------------------------------------------ relu(z)^2 in place
+template <typename T>
+__global__ void relu2_kernel(T* __restrict__ x, long count) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long)gridDim.x * blockDim.x) {
+        const float z = to_f32<T>(x[i]);
+        x[i] = from_f32<T>(z > 0.0f ? z * z : 0.0f);
+    }
+}
+
+KIRAI_EXPORT int kirai_relu2_f32(void* x, long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const unsigned blocks = (unsigned)min((count + 255) / 256, (long)148 * 16);
+    return launch_pdl(relu2_kernel<float>, dim3(blocks), dim3(256), 0, stream, 1u, (float*)x, count);
+}
+KIRAI_EXPORT int kirai_relu2_bf16(void* x, long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const unsigned blocks = (unsigned)min((count + 255) / 256, (long)148 * 16);
+    return launch_pdl(relu2_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, 1u, (bf16*)x, count);
+}
+
 // ------------------------------------------------------------ 32-bit -> bf16
 __global__ void round_rows_kernel(const float* __restrict__ src, bf16* __restrict__ dst, long count) {
     pdl_launch_dependents();

@@ -601,13 +601,13 @@ KIRAI_EXPORT int kirai_qkv_rope_write_bf16(const float* qkv, long qkv_stride, co
 // One block per token.  down row (float32): q_rank columns of the query latent, kv_rank of the key/value latent,
 // rot_dims of the key part that all heads share.  Both latents are divided by their root mean square (eps inside
 // the root) and multiplied by a weight per column; the shared key part is rotated whole (column i with column
-// i + rot_dims / 2).  The query latent leaves as [q_rank] in the runtime dtype; the page row of the token gets
+// i + rot_dims / 2, cosine and sine times rot_amp).  The query latent leaves as [q_rank] in the runtime dtype; the page row of the token gets
 // [latent, rotated part] as its key row and [latent] as its value row (cache [pages, 2, 1, page, dpad], the rest of
 // a row stays zero).
 template <typename T>
 __global__ void latent_prepare_kernel(const float* __restrict__ down, long down_stride, const float* __restrict__ q_weight,
-                                      const float* __restrict__ kv_weight, const float* __restrict__ inv_freq, float eps,
-                                      T* __restrict__ q_latent, T* __restrict__ cache, const int* __restrict__ block_table,
+                                      const float* __restrict__ kv_weight, const float* __restrict__ inv_freq, float rot_amp,
+                                      float eps, T* __restrict__ q_latent, T* __restrict__ cache, const int* __restrict__ block_table,
                                       const int* __restrict__ request_of_token, const int* __restrict__ positions, int q_rank,
                                       int kv_rank, int rot_dims, int dpad, int page_size, int table_width, int num_pages,
                                       int* __restrict__ error_flag) {
@@ -651,6 +651,8 @@ __global__ void latent_prepare_kernel(const float* __restrict__ down, long down_
         const float u = shared_part[i], v = shared_part[i + half];
         float sn, cs;
         sincosf(pos * inv_freq[i], &sn, &cs);
+        sn *= rot_amp;
+        cs *= rot_amp;
         key[kv_rank + i] = from_f32<T>(u * cs - v * sn);
         key[kv_rank + i + half] = from_f32<T>(v * cs + u * sn);
     }
@@ -658,7 +660,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ down, long down_
 
 template <typename T>
 static int latent_prepare_launch(const float* down, long down_stride, const float* q_weight, const float* kv_weight,
-                                 const float* inv_freq, float eps, void* q_latent, void* cache, const int* block_table,
+                                 const float* inv_freq, float rot_amp, float eps, void* q_latent, void* cache, const int* block_table,
                                  const int* request_of_token, const int* positions, int tokens, int q_rank, int kv_rank,
                                  int rot_dims, int dpad, int page_size, int table_width, int num_pages, int* error_flag,
                                  cudaStream_t stream) {
@@ -667,27 +669,112 @@ static int latent_prepare_launch(const float* down, long down_stride, const floa
         return KIRAI_ERR_BAD_SIZE;
     const int threads = (q_rank + kv_rank) >= 1024 ? 256 : 128;
     return launch_pdl(latent_prepare_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 1u, down, down_stride, q_weight, kv_weight,
-                      inv_freq, eps, (T*)q_latent, (T*)cache, block_table, request_of_token, positions, q_rank, kv_rank, rot_dims,
+                      inv_freq, rot_amp, eps, (T*)q_latent, (T*)cache, block_table, request_of_token, positions, q_rank, kv_rank, rot_dims,
                       dpad, page_size, table_width, num_pages, error_flag);
 }
 
 KIRAI_EXPORT int kirai_latent_prepare_f32(const float* down, long down_stride, const float* q_weight, const float* kv_weight,
-                                          const float* inv_freq, float eps, void* q_latent, void* cache, const int* block_table,
+                                          const float* inv_freq, float rot_amp, float eps, void* q_latent, void* cache, const int* block_table,
                                           const int* request_of_token, const int* positions, int tokens, int q_rank,
                                           int kv_rank, int rot_dims, int dpad, int page_size, int table_width, int num_pages,
                                           int* error_flag, cudaStream_t stream) {
-    return latent_prepare_launch<float>(down, down_stride, q_weight, kv_weight, inv_freq, eps, q_latent, cache, block_table,
+    return latent_prepare_launch<float>(down, down_stride, q_weight, kv_weight, inv_freq, rot_amp, eps, q_latent, cache, block_table,
                                         request_of_token, positions, tokens, q_rank, kv_rank, rot_dims, dpad, page_size,
                                         table_width, num_pages, error_flag, stream);
 }
 KIRAI_EXPORT int kirai_latent_prepare_bf16(const float* down, long down_stride, const float* q_weight, const float* kv_weight,
-                                           const float* inv_freq, float eps, void* q_latent, void* cache, const int* block_table,
+                                           const float* inv_freq, float rot_amp, float eps, void* q_latent, void* cache, const int* block_table,
                                            const int* request_of_token, const int* positions, int tokens, int q_rank,
                                            int kv_rank, int rot_dims, int dpad, int page_size, int table_width, int num_pages,
                                            int* error_flag, cudaStream_t stream) {
-    return latent_prepare_launch<bf16>(down, down_stride, q_weight, kv_weight, inv_freq, eps, q_latent, cache, block_table,
+    return latent_prepare_launch<bf16>(down, down_stride, q_weight, kv_weight, inv_freq, rot_amp, eps, q_latent, cache, block_table,
                                        request_of_token, positions, tokens, q_rank, kv_rank, rot_dims, dpad, page_size,
                                        table_width, num_pages, error_flag, stream);
+}
+
+// ------------------------------------------------- a product per head, then a gate
+// x [T, heads, pad] holds K used columns a head; w [heads, N, K] one matrix a head; out [T, heads * N]:
+//   out[t, h * N + v] = (sum_k w[h, v, k] x[t, h, k]) * sigmoid(gate[t, h * N + v])        (no gate: the product alone)
+// in 32-bit accumulation.  This is what latent attention needs between its attention over the shared latent and its
+// output projection when the heads' values pass a gate: the heads' sums of latents go through each head's value
+// matrix.  A block takes HEAD_TOKENS tokens of one head and a run of output columns; the tokens' rows lie in shared
+// memory in 32-bit, a warp takes one output column at a time, its lanes stride over k (the matrix row is read
+// coalesced, once per block) and keep one partial sum a token.
+#define HEAD_TOKENS 16
+#define HEAD_K_PIECE 512
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_linear_gate_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ gate, long gate_stride,
+                        T* __restrict__ out, int tokens, int heads, int pad, int K, int N, int columns_a_block) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float rows_s[HEAD_TOKENS][HEAD_K_PIECE];
+    const int head = blockIdx.y;
+    const int first = blockIdx.x * HEAD_TOKENS;
+    const int count = min(HEAD_TOKENS, tokens - first);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int col_lo = blockIdx.z * columns_a_block, col_hi = min(N, col_lo + columns_a_block);
+    for (int v0 = col_lo; v0 < col_hi; v0 += warps) {
+        // every warp walks the same k pieces, so the block meets at the barriers whatever its column
+        const int v = v0 + warp;
+        float acc[HEAD_TOKENS];
+#pragma unroll
+        for (int t = 0; t < HEAD_TOKENS; ++t) acc[t] = 0.0f;
+        for (int k0 = 0; k0 < K; k0 += HEAD_K_PIECE) {
+            const int piece = min(HEAD_K_PIECE, K - k0);
+            if (K > HEAD_K_PIECE || v0 == col_lo) {
+                __syncthreads();
+                for (int i = threadIdx.x; i < HEAD_TOKENS * piece; i += blockDim.x) {
+                    const int t = i / piece, k = i - t * piece;
+                    rows_s[t][k] = t < count ? to_f32<T>(x[((size_t)(first + t) * heads + head) * pad + k0 + k]) : 0.0f;
+                }
+                __syncthreads();
+            }
+            if (v < col_hi) {
+                const T* row = w + ((size_t)head * N + v) * K + k0;
+                for (int k = lane; k < piece; k += 32) {
+                    const float weight = to_f32<T>(row[k]);
+#pragma unroll
+                    for (int t = 0; t < HEAD_TOKENS; ++t) acc[t] = fmaf(weight, rows_s[t][k], acc[t]);
+                }
+            }
+        }
+        if (v < col_hi) {
+#pragma unroll
+            for (int t = 0; t < HEAD_TOKENS; ++t) {
+                const float total = warp_sum(acc[t]);
+                if (lane == (t & 31) && t < count) {
+                    const size_t at = (size_t)head * N + v;
+                    float value = total;
+                    if (gate) value *= 1.0f / (1.0f + expf(-gate[(size_t)(first + t) * gate_stride + at]));
+                    out[(size_t)(first + t) * heads * N + at] = from_f32<T>(value);
+                }
+            }
+        }
+    }
+}
+
+template <typename T>
+static int head_linear_gate_launch(const void* x, const void* w, const float* gate, long gate_stride, void* out, int tokens,
+                                   int heads, int pad, int K, int N, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || K <= 0 || N <= 0 || pad < K) return KIRAI_ERR_BAD_SIZE;
+    const int tiles = (tokens + HEAD_TOKENS - 1) / HEAD_TOKENS;
+    // few tokens: a head's columns are cut over several blocks, so that the matrices are read by enough of them
+    int cuts = 1;
+    while ((long)tiles * heads * cuts < 296 && N / (cuts * 2) >= 8 && cuts < 64) cuts *= 2;
+    const int columns = (N + cuts - 1) / cuts;
+    return launch_pdl(head_linear_gate_kernel<T>, dim3(tiles, heads, (N + columns - 1) / columns), dim3(256), 0, stream, 1u,
+                      (const T*)x, (const T*)w, gate, gate_stride, (T*)out, tokens, heads, pad, K, N, columns);
+}
+
+KIRAI_EXPORT int kirai_head_linear_gate_f32(const void* x, const void* w, const float* gate, long gate_stride, void* out, int tokens,
+                                            int heads, int pad, int K, int N, cudaStream_t stream) {
+    return head_linear_gate_launch<float>(x, w, gate, gate_stride, out, tokens, heads, pad, K, N, stream);
+}
+KIRAI_EXPORT int kirai_head_linear_gate_bf16(const void* x, const void* w, const float* gate, long gate_stride, void* out, int tokens,
+                                             int heads, int pad, int K, int N, cudaStream_t stream) {
+    return head_linear_gate_launch<bf16>(x, w, gate, gate_stride, out, tokens, heads, pad, K, N, stream);
 }
 
 // ------------------------------------------------------------- element-wise steps
@@ -754,8 +841,10 @@ __device__ __forceinline__ float gelu_tanh_f32(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// act 2: g' = min(gate, limit), u' = clamp(up, -limit, limit), g' * sigmoid(slope * g') * (u' + 1).
 template <typename T>
-__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long rows, int inter, int act) {
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long rows, int inter, int act,
+                                        float limit, float slope) {
     pdl_launch_dependents();
     pdl_wait();
     const long total = rows * inter;
@@ -764,27 +853,34 @@ __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __rest
         const int c = (int)(at - row * inter);
         const float g = to_f32<T>(gate_up[row * 2 * inter + c]);
         const float u = to_f32<T>(gate_up[row * 2 * inter + inter + c]);
+        if (act == 2) {
+            out[at] = from_f32<T>(clamped_gated_f32(g, u, limit, slope));
+            continue;
+        }
         const float a = act == 1 ? gelu_tanh_f32(g) : g * sigmoid_f32(g);
         out[at] = from_f32<T>(a * u);
     }
 }
 
 template <typename T>
-static int gated_activation_launch(const void* gate_up, void* out, int rows, int inter, int act, cudaStream_t stream) {
+static int gated_activation_launch(const void* gate_up, void* out, int rows, int inter, int act, float limit, float slope,
+                                   cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (inter <= 0 || act < 0 || act > 1) return KIRAI_ERR_BAD_SIZE;
+    if (inter <= 0 || act < 0 || act > 2 || (act == 2 && !(limit > 0.0f))) return KIRAI_ERR_BAD_SIZE;
     const long total = (long)rows * inter;
     const int threads = 256;
     const unsigned blocks = (unsigned)min((total + threads - 1) / threads, (long)148 * 16);
     return launch_pdl(gated_activation_kernel<T>, dim3(blocks), dim3(threads), 0, stream, 1u, (const T*)gate_up, (T*)out, (long)rows,
-                      inter, act);
+                      inter, act, limit, slope);
 }
 
-KIRAI_EXPORT int kirai_gated_activation_f32(const void* gate_up, void* out, int rows, int inter, int act, cudaStream_t stream) {
-    return gated_activation_launch<float>(gate_up, out, rows, inter, act, stream);
+KIRAI_EXPORT int kirai_gated_activation_f32(const void* gate_up, void* out, int rows, int inter, int act, float limit, float slope,
+                                            cudaStream_t stream) {
+    return gated_activation_launch<float>(gate_up, out, rows, inter, act, limit, slope, stream);
 }
-KIRAI_EXPORT int kirai_gated_activation_bf16(const void* gate_up, void* out, int rows, int inter, int act, cudaStream_t stream) {
-    return gated_activation_launch<bf16>(gate_up, out, rows, inter, act, stream);
+KIRAI_EXPORT int kirai_gated_activation_bf16(const void* gate_up, void* out, int rows, int inter, int act, float limit, float slope,
+                                             cudaStream_t stream) {
+    return gated_activation_launch<bf16>(gate_up, out, rows, inter, act, limit, slope, stream);
 }
 
 // x [T, width] (in place) += bias [width] (float32).

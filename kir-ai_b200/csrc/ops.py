@@ -309,6 +309,67 @@ def norm_add(resid: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: fl
     return copy
 
 
+def norm_add_norm(resid: torch.Tensor, y: torch.Tensor, weight_add: torch.Tensor, eps_add: float, weight_next: torch.Tensor,
+                  eps_next: float, out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The norm on a sub-layer's output and the norm that reads the stream next, in one pass: ``resid`` (32-bit, in
+    place) += RMSNorm(``y``) with ``weight_add``; returns RMSNorm(the sum) with ``weight_next`` in ``out_dtype``.  With
+    ``row_index`` only those rows are produced and the stream is left as it is."""
+    _need_cuda(resid, y, weight_add, weight_next, row_index)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
+    assert y.dtype == torch.float32 and y.shape == resid.shape and y.is_contiguous()
+    hidden = resid.shape[1]
+    for weight in (weight_add, weight_next):
+        assert weight.dtype == torch.float32 and weight.numel() == hidden and weight.is_contiguous()
+    rows = resid.shape[0] if row_index is None else row_index.numel()
+    if row_index is not None:
+        assert row_index.dtype == torch.int32 and row_index.is_contiguous()
+    out = torch.empty((rows, hidden), dtype=out_dtype, device=resid.device)
+    _call(f"kirai_norm_add_norm_{_suffix(out_dtype)}", _ptr(resid), _ptr(y), _ptr(weight_add), _ptr(weight_next), _ptr(out),
+          _ptr(row_index), _i(rows), _i(hidden), _f(eps_add), _f(eps_next), _stream())
+    return out
+
+
+def stream_copy(resid: torch.Tensor, out: torch.Tensor, y: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None,
+                eps: float = 0.0) -> torch.Tensor:
+    """``out`` [T, H] (a run of columns of a wider buffer is allowed) receives the stream ``resid`` [T, H] (32-bit) in
+    its own dtype; with ``y`` the stream first takes RMSNorm(``y``) with ``weight`` (in place), as ``norm_add`` does."""
+    _need_cuda(resid, out, y, weight)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
+    assert out.dim() == 2 and out.shape == resid.shape and out.stride(1) == 1
+    if y is not None:
+        assert y.dtype == torch.float32 and y.shape == resid.shape and y.is_contiguous()
+        assert weight is not None and weight.dtype == torch.float32 and weight.numel() == resid.shape[1] and weight.is_contiguous()
+    _call(f"kirai_stream_copy_{_suffix(out.dtype)}", _ptr(resid), _ptr(y), _ptr(weight), _ptr(out), _l(out.stride(0)),
+          _i(resid.shape[0]), _i(resid.shape[1]), _f(eps), _stream())
+    return out
+
+
+def relu2_(x: torch.Tensor) -> torch.Tensor:
+    """``x`` (in place) <- relu(x)^2."""
+    _need_cuda(x)
+    assert x.is_contiguous()
+    _call(f"kirai_relu2_{_suffix(x.dtype)}", _ptr(x), _l(x.numel()), _stream())
+    return x
+
+
+def head_linear_gate(x: torch.Tensor, weight: torch.Tensor, heads: int, used: int, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A product per head: ``x`` [T, heads * pad] (the first ``used`` columns of every head count), ``weight``
+    [heads, N, used] in the dtype of ``x``; returns [T, heads * N], row t's head h = weight[h] x[t, h], times
+    sigmoid(``gate`` [T, heads * N]) where a gate is given (float32; a run of columns of a wider product is allowed)."""
+    _need_cuda(x, weight, gate)
+    assert x.dim() == 2 and x.is_contiguous() and x.shape[1] % heads == 0
+    pad = x.shape[1] // heads
+    assert weight.dim() == 3 and weight.is_contiguous() and weight.dtype == x.dtype and weight.shape[0] == heads and weight.shape[2] == used <= pad
+    n = weight.shape[1]
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == (x.shape[0], heads * n)
+    out = torch.empty((x.shape[0], heads * n), dtype=x.dtype, device=x.device)
+    _call(f"kirai_head_linear_gate_{_suffix(x.dtype)}", _ptr(x), _ptr(weight), _ptr(gate), _l(gate.stride(0) if gate is not None else 0),
+          _ptr(out), _i(x.shape[0]), _i(heads), _i(pad), _i(used), _i(n), _stream(),
+          detail=f" t={x.shape[0]} heads={heads} k={used} n={n}" if _timer is not None else "")
+    return out
+
+
 def round_rows(x: torch.Tensor) -> torch.Tensor:
     """The 32-bit rows ``x`` rounded to bfloat16."""
     _need_cuda(x)
@@ -459,14 +520,15 @@ def qkv_rope_write(qkv: torch.Tensor, q_heads: int, kv_heads: int, key_dim: int,
 def latent_prepare(down: torch.Tensor, q_rank: int, kv_rank: int, rot_dims: int, q_weight: Optional[torch.Tensor],
                    kv_weight: torch.Tensor, inv_freq: Optional[torch.Tensor], eps: float, cache: torch.Tensor,
                    block_table: torch.Tensor, request_of_token: torch.Tensor, positions: torch.Tensor,
-                   out_dtype: torch.dtype) -> torch.Tensor:
-    """Prepares latent attention from ``down`` [T, q_rank + kv_rank + rot_dims] (float32, the stacked down
-    projections): both latents get their RMS norm (a weight per column, ``eps`` inside the root), the last
-    ``rot_dims`` columns, the key part that all heads share, are rotated whole by position * inv_freq, and the token's
+                   out_dtype: torch.dtype, rot_amplitude: float = 1.0) -> torch.Tensor:
+    """Prepares latent attention from ``down`` [T, >= q_rank + kv_rank + rot_dims] (float32, the stacked down
+    projections; further columns are left alone): both latents get their RMS norm (a weight per column, ``eps`` inside
+    the root), the ``rot_dims`` columns behind them, the key part that all heads share, are rotated whole by position *
+    inv_freq (cosine and sine times ``rot_amplitude``), and the token's
     page row in ``cache`` [pages, 2, 1, page, pad] gets [latent, rotated part] as its key row and [latent] as its value
     row.  Returns the normed query latent [T, q_rank] in ``out_dtype``."""
     _need_cuda(down, q_weight, kv_weight, inv_freq, cache, block_table, request_of_token, positions)
-    assert down.dtype == torch.float32 and down.dim() == 2 and down.stride(1) == 1 and down.shape[1] == q_rank + kv_rank + rot_dims
+    assert down.dtype == torch.float32 and down.dim() == 2 and down.stride(1) == 1 and down.shape[1] >= q_rank + kv_rank + rot_dims
     for t, n in ((q_weight, q_rank), (kv_weight, kv_rank), (inv_freq, rot_dims // 2)):
         assert t is None or (t.dtype == torch.float32 and t.numel() == n and t.is_contiguous())
     num_pages, c_heads, page_size, pad_dim = _cache_dims(cache)
@@ -474,7 +536,7 @@ def latent_prepare(down: torch.Tensor, q_rank: int, kv_rank: int, rot_dims: int,
     tokens = down.shape[0]
     q_latent = torch.empty((tokens, q_rank), dtype=out_dtype, device=down.device)
     _call(f"kirai_latent_prepare_{_suffix(out_dtype)}", _ptr(down), _l(down.stride(0)), _ptr(q_weight), _ptr(kv_weight),
-          _ptr(inv_freq if rot_dims else None), _f(eps), _ptr(q_latent), _ptr(cache), _ptr(block_table), _ptr(request_of_token),
+          _ptr(inv_freq if rot_dims else None), _f(rot_amplitude), _f(eps), _ptr(q_latent), _ptr(cache), _ptr(block_table), _ptr(request_of_token),
           _ptr(positions), _i(tokens), _i(q_rank), _i(kv_rank), _i(rot_dims), _i(pad_dim), _i(page_size),
           _i(block_table.shape[1]), _i(num_pages), _ptr(error_flag(down.device)), _stream())
     return q_latent
@@ -491,18 +553,19 @@ def sigmoid_gate_(x: torch.Tensor, gate: torch.Tensor, heads: int, used: int, pa
     return x
 
 
-GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped": 2}
 
 
-def gated_activation(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
+def gated_activation(gate_up: torch.Tensor, activation: str, limit: float = 0.0, slope: float = 1.0) -> torch.Tensor:
     """act(gate) * up for ``gate_up`` [T, 2 I] (gate half first); ``activation`` is ``silu`` or ``gelu_tanh``
-    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))).  Returns [T, I]."""
+    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))), or ``clamped``: with g = min(gate, limit) and
+    u = clamp(up, -limit, limit) the result is g * sigmoid(slope * g) * (u + 1).  Returns [T, I]."""
     _need_cuda(gate_up)
     assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
     rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
     out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
     _call(f"kirai_gated_activation_{_suffix(gate_up.dtype)}", _ptr(gate_up), _ptr(out), _i(rows), _i(inter),
-          _i(GATED_ACTIVATIONS[activation]), _stream())
+          _i(GATED_ACTIVATIONS[activation]), _f(limit), _f(slope), _stream())
     return out
 
 
@@ -701,16 +764,18 @@ def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
     return x
 
 
-def gated_expert_gate(gate_up: torch.Tensor, gates: torch.Tensor, ff: int, activation: str = "silu") -> torch.Tensor:
+def gated_expert_gate(gate_up: torch.Tensor, gates: torch.Tensor, ff: int, activation: str = "silu", limit: float = 0.0,
+                      slope: float = 1.0) -> torch.Tensor:
     """Stacked gated experts: ``gate_up`` [T, experts * 2 ff] (per expert ff gate columns, then ff up columns) becomes
-    [T, experts * ff] = act(gate) * up * gates[t, expert] (``gates`` float32 [T, experts], zero where not chosen)."""
+    [T, experts * ff] = act(gate) * up * gates[t, expert] (``gates`` float32 [T, experts], zero where not chosen);
+    the activations are those of ``gated_activation``."""
     _need_cuda(gate_up, gates)
     assert gate_up.dim() == 2 and gate_up.is_contiguous() and gates.dtype == torch.float32 and gates.is_contiguous()
     experts = gates.shape[1]
     assert gate_up.shape == (gates.shape[0], experts * 2 * ff)
     out = torch.empty((gate_up.shape[0], experts * ff), dtype=gate_up.dtype, device=gate_up.device)
     _call(f"kirai_gated_expert_gate_{_suffix(gate_up.dtype)}", _ptr(gate_up), _ptr(gates), _ptr(out), _i(gate_up.shape[0]),
-          _i(experts), _i(ff), _i(GATED_ACTIVATIONS[activation]), _stream())
+          _i(experts), _i(ff), _i(GATED_ACTIVATIONS[activation]), _f(limit), _f(slope), _stream())
     return out
 
 
@@ -732,12 +797,28 @@ def _router_arrivals(device: torch.device, tokens: int) -> torch.Tensor:
     return counters
 
 
-def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: bool = False, over_all: bool = False):
+def _router_rule(over_all: bool, rule: Optional[dict], experts: int, device):
+    """The kernels' arguments for how weights come from logits: (mode, correction, groups, keep).  ``rule`` is None
+    (softmax over the chosen logits, or over all with ``over_all``) or a dict with ``correction`` (a tensor [experts],
+    float32, or None), ``groups`` and ``keep``: sigmoid scores, the choice by score + correction among the ``keep``
+    best of ``groups`` equal groups of neighbouring experts (a group's mark is the sum of its two largest choice
+    scores), the weights the chosen scores as they are."""
+    if rule is None:
+        return _i(int(over_all)), _ptr(None), _i(1), _i(1)
+    correction = rule.get("correction")
+    if correction is not None:
+        _need_cuda(correction)
+        assert correction.dtype == torch.float32 and correction.numel() == experts and correction.is_contiguous()
+    return _i(2), _ptr(correction), _i(int(rule.get("groups", 1))), _i(int(rule.get("keep", 1)))
+
+
+def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: bool = False, over_all: bool = False,
+                 rule: Optional[dict] = None):
     """Routing weights of every token: logits ``router`` [experts, H] (float32) times ``x`` [T, H] in 32-bit, the ``top``
     largest chosen (the lower index on a tie), softmax over the chosen logits alone.  Returns gates [T, experts]
     (float32, zero where not chosen); with ``want_chosen`` also (ids [T, top] int32, weights [T, top] float32) in the
     order of choice.  ``over_all``: the weights are the chosen experts' shares of the softmax over ALL logits instead
-    (they then do not sum to one)."""
+    (they then do not sum to one).  ``rule``: sigmoid scores with a correction and groups, see ``_router_rule``."""
     _need_cuda(x, router)
     assert x.dim() == 2 and x.stride(1) == 1 and router.dtype == torch.float32 and router.is_contiguous()
     assert router.shape[1] == x.shape[1] and 0 < top <= router.shape[0]
@@ -746,11 +827,12 @@ def router_gates(x: torch.Tensor, router: torch.Tensor, top: int, want_chosen: b
     ids = torch.empty((tokens, top), dtype=torch.int32, device=x.device) if want_chosen else None
     weights = torch.empty((tokens, top), dtype=torch.float32, device=x.device) if want_chosen else None
     _call(f"kirai_router_gates_{_suffix(x.dtype)}", _ptr(x), _l(x.stride(0)), _ptr(router), _ptr(gates), _ptr(ids), _ptr(weights),
-          _ptr(_router_arrivals(x.device, tokens)), _i(tokens), _i(x.shape[1]), _i(experts), _i(top), _i(int(over_all)), _stream())
+          _ptr(_router_arrivals(x.device, tokens)), _i(tokens), _i(x.shape[1]), _i(experts), _i(top),
+          *_router_rule(over_all, rule, experts, x.device), _stream())
     return (gates, ids, weights) if want_chosen else gates
 
 
-def router_choose_(logits: torch.Tensor, top: int, want_chosen: bool = False, over_all: bool = False):
+def router_choose_(logits: torch.Tensor, top: int, want_chosen: bool = False, over_all: bool = False, rule: Optional[dict] = None):
     """The choice alone: ``logits`` [T, experts] (float32, as a product left them) become the routing weights in place
     (see ``router_gates``).  Returns what ``router_gates`` returns."""
     _need_cuda(logits)
@@ -758,7 +840,8 @@ def router_choose_(logits: torch.Tensor, top: int, want_chosen: bool = False, ov
     tokens, experts = logits.shape
     ids = torch.empty((tokens, top), dtype=torch.int32, device=logits.device) if want_chosen else None
     weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device) if want_chosen else None
-    _call("kirai_router_choose", _ptr(logits), _ptr(ids), _ptr(weights), _i(tokens), _i(experts), _i(top), _i(int(over_all)), _stream())
+    _call("kirai_router_choose", _ptr(logits), _ptr(ids), _ptr(weights), _i(tokens), _i(experts), _i(top),
+          *_router_rule(over_all, rule, experts, logits.device), _stream())
     return (logits, ids, weights) if want_chosen else logits
 
 

@@ -16,7 +16,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..parts.base import Norm, Runtime, ScaledSum, StreamCopy, WeightSpec
+from ..parts.base import Norm, NormedSum, Runtime, ScaledSum, StreamCopy, WeightSpec
 from ..parts.block import Block
 from ..parts.embedding import Embedding, OutputHead
 
@@ -26,12 +26,15 @@ class LayerCall:
     """Run ``block`` with cache layer ``cache`` (None: the mixer keeps nothing; a tuple of cache layers for a mixer
     whose ``cache_need()`` is a tuple of needs, as two mixers side by side of which one keeps pages and one a state);
     ``write`` false reads what an earlier call wrote in the same step.  ``shift_cache`` is the cache layer of the
-    block's token shift, where it has one (a state slot per request; every call has its own)."""
+    block's token shift, where it has one (a state slot per request; every call has its own).  ``enter`` = (index
+    into the plan's ``entries``, row of its bias table): ahead of this call the stream starts over from itself and the
+    embedding's rows (``parts.merge.StreamMerge``), as at the head of every pass of a looped stretch."""
 
     block: int
     cache: object = None
     write: bool = True
     shift_cache: Optional[int] = None
+    enter: Optional[tuple] = None
 
 
 class PlanError(ValueError):
@@ -50,6 +53,7 @@ class ModelPlan:
     max_positions: Optional[int] = None
     ignorable_weights: List[str] = field(default_factory=list)  # tensors a folder may hold that no part wants
     cache_needs: List[object] = field(default_factory=list)  # filled by validate(): one need per cache layer
+    entries: List[object] = field(default_factory=list)  # parts that stand between blocks (``LayerCall.enter``)
 
     def validate(self) -> "ModelPlan":
         """Checks the order against the blocks and derives the need of every cache layer."""
@@ -57,6 +61,8 @@ class ModelPlan:
         for step, call in enumerate(self.order):
             if not 0 <= call.block < len(self.blocks):
                 raise PlanError(f"order[{step}] names block {call.block}, but there are {len(self.blocks)} blocks")
+            if call.enter is not None and not 0 <= call.enter[0] < len(self.entries):
+                raise PlanError(f"order[{step}] enters through part {call.enter[0]}, but there are {len(self.entries)} such parts")
             shift_need = getattr(self.blocks[call.block], "shift_need", lambda: None)()
             if (shift_need is None) != (call.shift_cache is None):
                 raise PlanError(f"order[{step}]: block {call.block} {'needs' if shift_need is not None else 'has no use for'} a cache layer for its token shift")
@@ -97,7 +103,7 @@ class ModelPlan:
         return self
 
     def parts(self):
-        return [self.embedding, *self.blocks, self.final_norm, self.head]
+        return [self.embedding, *self.entries, *self.blocks, self.final_norm, self.head]
 
     def capture_safe(self) -> bool:
         """Whether a step of single tokens may be recorded into a CUDA graph: every part promises it
@@ -127,6 +133,7 @@ class DecoderModel:
         self.rt = rt
         # with parts that touch activations through the kernels only, a step's small products are launched together
         self._kernels_only = plan.kernels_only() and hasattr(rt.ops, "chained_products")
+        self._entered = sorted({call.enter[0] for call in plan.order if call.enter is not None})
         self.nvtx = False  # True: every layer call is an NVTX range (the reference counts attempts and fallbacks per
         # kernel instead, crates/llm-native-runtime/src/native_metrics.rs:7-70; here ops.launch_counts does that)
 
@@ -149,7 +156,11 @@ class DecoderModel:
                 resid = embedding.forward(batch.token_ids, batch.positions)
             else:
                 resid = embedding.forward(batch.token_ids)
+            # every part that stands between blocks takes the embedding's rows now, before a block changes the stream
+            pairs = {index: self.plan.entries[index].begin(resid) for index in self._entered}
             for i, call in enumerate(order):
+                if call.enter is not None:
+                    resid, delta = self.plan.entries[call.enter[0]].forward(resid, delta, pairs[call.enter[0]], call.enter[1])
                 if isinstance(call.cache, tuple):
                     view = tuple(cache.layer_view(layer) for layer in call.cache)
                 else:
@@ -170,6 +181,9 @@ class DecoderModel:
         """32-bit logits [len(rows), V] of the token rows ``rows`` (int32, on the device)."""
         if isinstance(delta, StreamCopy):
             delta = None  # the last block left the stream complete
+        if isinstance(delta, NormedSum) and not getattr(self.plan.final_norm, "takes_normed_sum", False):
+            delta.settle(resid, self.rt.ops)
+            delta = None
         if isinstance(delta, ScaledSum) and not getattr(self.plan.final_norm, "takes_scaled_sum", False):
             self.rt.ops.add_scaled_into_residual(resid, delta.rows, delta.factor)
             delta = None

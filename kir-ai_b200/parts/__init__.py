@@ -7,6 +7,8 @@ from .experts import RoutedExperts
 from .latent import LatentAttention
 from .linear import Linear
 from .matrix_memory import MatrixMemory
+from .merge import StreamMerge
+from .mlp import PlainMLP
 from .mingru import MinGRU
 from .norm import DynamicTanh, LayerNorm, RMSNorm
 from .rope import RotaryEmbedding
@@ -18,4 +20,4 @@ from .swiglu import GatedMLP, SwiGLU
 __all__ = ["GQAttention", "FeedForward", "KVCacheNeed", "Mixer", "Norm", "Part", "PositionEncoding", "Runtime",
            "StateNeed", "StreamCopy", "WeightSpec", "RoutedExperts", "Block", "Embedding", "OutputHead", "Linear", "RMSNorm", "RotaryEmbedding", "SwiGLU",
            "GatedMLP", "LatentAttention", "LayerNorm", "MinGRU", "TokenShift", "DynamicTanh", "MatrixMemory", "SideBySideMixer",
-           "StateSpaceMixer"]
+           "StateSpaceMixer", "StreamMerge", "PlainMLP"]

@@ -39,7 +39,9 @@ projection (the matrix rides in the stacked q, k, v product); ``out_bias`` names
 h's output (it rides in the stacked product too).  ``keep_first`` F goes with a ``window`` W: position i sees j <= i
 when i - j < W or j < F, so a sequence's first F keys stay visible at their true positions (the cache keeps their
 pages when the window gives the others back).  A ``RotaryEmbedding`` whose cosine and sine carry a factor
-(``amplitude``) is applied with it by the preparation kernel.
+(``amplitude``) is applied with it by the preparation kernel.  A ``RotaryEmbedding`` that pairs neighbouring columns
+has the rows of the q and k matrices (and biases) put in its ``head_order`` at load; scores do not change with the
+order of a head's columns, as long as queries and keys share it.
 """
 from __future__ import annotations
 
@@ -98,7 +100,8 @@ class GQAttention(Mixer):
         self.out_bias_name = prefix + out_bias if out_bias else None
         self.head_factor = self.out_bias = None
         self.defer_output_bias = False  # a block whose next norm adds the bias sets this
-        shifted_rotation = isinstance(position, RotaryEmbedding) and (position.offset != 0 or position.amplitude != 1.0)
+        shifted_rotation = isinstance(position, RotaryEmbedding) and (position.offset != 0 or position.amplitude != 1.0
+                                                                      or position.pairing != "halves")
         self.wide = (head_gate is not None or self.keep_first > 0 or bias or self.value_dim != head_dim or (qk_norm_eps is not None and qk_norm_over == "projection")
                      or head_factor is not None or gate is not None or shifted_rotation or self.softcap is not None
                      or self.chunk is not None or out_bias is not None)
@@ -120,7 +123,20 @@ class GQAttention(Mixer):
             sources.append((self.gate_name, q_heads * self.value_dim))
         if self.head_gate_name:
             sources.append((self.head_gate_name, q_heads))
-        self.qkv = Linear(sources, hidden_size)
+        # a rotation that pairs neighbouring columns: queries and keys are projected with their columns in the kernels' order
+        self.q_order = self.k_order = None
+        stacked_order = None
+        if isinstance(position, RotaryEmbedding) and position.head_order() is not None:
+            if not self.wide:
+                raise ValueError("a rotation of neighbouring columns is built for the preparation that takes biases and partial rotations")
+            self.q_order = position.row_order(q_heads)
+            self.k_order = None if reads_only else position.row_order(kv_heads)
+            total = sum(rows for _, rows in sources)
+            stacked_order = torch.arange(total)
+            stacked_order[: q_heads * head_dim] = self.q_order
+            if self.k_order is not None:
+                stacked_order[q_heads * head_dim : (q_heads + kv_heads) * head_dim] = q_heads * head_dim + self.k_order
+        self.qkv = Linear(sources, hidden_size, row_order=stacked_order)
         self.out = Linear([(prefix + n["o"], hidden_size)], q_heads * self.value_dim,
                           column_groups=(q_heads, self.value_dim, self.pad_dim) if self.wide else None)
         self.q_norm_name, self.k_norm_name = prefix + n["q_norm"], prefix + n["k_norm"]
@@ -174,8 +190,12 @@ class GQAttention(Mixer):
                 self.k_norm_weight = weights.on_device(self.k_norm_name, torch.float32)
         if self.bias:
             self.q_bias = weights.on_device(self.bias_names[0], torch.float32)
+            if self.q_order is not None:
+                self.q_bias = self.q_bias[self.q_order.to(rt.device)].contiguous()
             if not self.reads_only:
                 self.k_bias = weights.on_device(self.bias_names[1], torch.float32)
+                if self.k_order is not None:
+                    self.k_bias = self.k_bias[self.k_order.to(rt.device)].contiguous()
                 self.v_bias = weights.on_device(self.bias_names[2], torch.float32)
         if self.head_factor_name:
             self.head_factor = weights.on_device(self.head_factor_name, torch.float32)

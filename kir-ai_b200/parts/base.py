@@ -101,6 +101,22 @@ class ScaledSum:
     factor: float
 
 
+@dataclass
+class NormedSum:
+    """What a sub-layer leaves to be added into the stream when the block norms its OUTPUT and the next reader of the
+    stream is a norm again: ``rows`` (float32 [T, width]) divided by their root mean square (``eps`` inside the root)
+    times ``weight`` [width].  A norm that ``takes_normed_sum`` adds it and norms the sum in one pass over the row; for
+    any other reader ``settle`` adds it into the stream first."""
+
+    rows: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+
+    def settle(self, resid: torch.Tensor, ops, copy_dtype: Optional[torch.dtype] = None):
+        """resid += norm(rows) in place; returns the stream's copy in ``copy_dtype`` when that is asked for."""
+        return ops.norm_add(resid, self.rows, self.weight, self.eps, copy_dtype)
+
+
 class Runtime:
     """Where and in which precision a model runs: the device, the dtype of
     weights and activations (``torch.float32`` for the true 32-bit path,

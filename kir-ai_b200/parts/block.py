@@ -22,6 +22,13 @@ mixed with the row of the token before.  The shift keeps a request's last row in
 layer call's ``shift_cache``), the norm hands it 32-bit rows, and the first norm then stays a kernel.  A mixer whose
 output projection has a bias may leave it to the norm that adds its output into the stream (``deferred_bias``).
 
+``sandwich`` norms both what a sub-layer reads and what it produced: h' = h + post1(mixer(norm1(h)));
+out = h' + post2(ffn(norm2(h'))), with the norms on the outputs given as ``post_norm1`` and ``post_norm2``; the
+feed-forward with its two norms may be missing.  The sub-layers leave 32-bit rows.  The norm on an output and the norm
+that reads the stream next are one pass over the row: the block hands what is left to add on as a ``NormedSum``, which
+a norm that ``takes_normed_sum`` adds while it norms (the next sub-layer's, the next block's first, or the model's
+last); any other reader has it settled into the stream first.
+
 ``residual_scale`` m (``pre_norm`` only) multiplies what every sub-layer adds: h <- h + m * mixer(norm1(h)), then
 h <- h + m * ffn(norm2(h)).  The sub-layers then leave 32-bit rows (a feed-forward may leave several terms,
 ``FeedForward.forward_terms``), which travel to the next norm as a ``ScaledSum``; a norm that ``takes_scaled_sum`` adds
@@ -29,13 +36,14 @@ them in its own pass, for any other a kernel adds them first.  No norm is folded
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
 
-from .base import FeedForward, FusedNormSpec, Mixer, Norm, Part, Runtime, ScaledSum, StreamCopy, UnscaledNorm, WeightSpec
+from .base import FeedForward, FusedNormSpec, Mixer, Norm, NormedSum, Part, Runtime, ScaledSum, StreamCopy, UnscaledNorm, WeightSpec
 
-ARRANGEMENTS = ("pre_norm", "parallel", "out_norm")
+ARRANGEMENTS = ("pre_norm", "parallel", "out_norm", "sandwich")
 
 
 def _offers(part, method: str, rows: int) -> bool:
@@ -47,7 +55,13 @@ def _offers(part, method: str, rows: int) -> bool:
 
 class Block(Part):
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm], ffn: Optional[FeedForward], arrangement: str = "pre_norm",
-                 shift: Optional[Part] = None, residual_scale: Optional[float] = None):
+                 shift: Optional[Part] = None, residual_scale: Optional[float] = None, post_norm1: Optional[Norm] = None,
+                 post_norm2: Optional[Norm] = None):
+        if (arrangement == "sandwich") != (post_norm1 is not None) or (post_norm2 is not None) != (arrangement == "sandwich" and ffn is not None):
+            raise ValueError("the sandwich arrangement, and it alone, has a norm on every sub-layer's output")
+        if arrangement == "sandwich" and ((ffn is None) != (norm2 is None) or shift is not None):
+            raise ValueError("the sandwich arrangement has its second pair of norms exactly when it has a feed-forward, and no token shift")
+        self.post_norm1, self.post_norm2 = post_norm1, post_norm2
         if residual_scale is not None and (arrangement != "pre_norm" or shift is not None):
             raise ValueError("a factor on the sub-layers' outputs is built for the pre_norm arrangement without a token shift")
         self.residual_scale = None if residual_scale is None else float(residual_scale)
@@ -70,7 +84,7 @@ class Block(Part):
             mixer.defer_output_bias = True
 
     def _parts(self):
-        return [p for p in (self.norm1, self.shift, self.mixer, self.norm2, self.ffn) if p is not None]
+        return [p for p in (self.norm1, self.shift, self.mixer, self.post_norm1, self.norm2, self.ffn, self.post_norm2) if p is not None]
 
     def shift_need(self):
         """What the block's token shift keeps per request (None without one)."""
@@ -126,6 +140,11 @@ class Block(Part):
                                              or not getattr(self.norm1, "takes_scaled_sum", False)):
             self.rt.ops.add_scaled_into_residual(resid, delta.rows, delta.factor)
             delta = None
+        if isinstance(delta, NormedSum) and (self.arrangement != "sandwich" or not getattr(self.norm1, "takes_normed_sum", False)):
+            delta.settle(resid, self.rt.ops)
+            delta = None
+        if self.arrangement == "sandwich":
+            return self._forward_sandwich(resid, delta, batch, cache, write_cache)
         if self.residual_scale is not None:
             return self._forward_scaled(resid, delta, batch, cache, write_cache)
         if self.arrangement == "out_norm":
@@ -159,6 +178,27 @@ class Block(Part):
         m = self.ffn.forward(n, batch)
         self.norm1.rt.ops.add_into_residual(resid, a)
         return resid, m
+
+    def _forward_sandwich(self, resid, delta, batch, cache, write_cache):
+        """A norm before and after each sub-layer; what the last norm makes is left to the next reader of the stream."""
+        if isinstance(delta, UnscaledNorm):
+            raise ValueError("a sandwich block cannot follow a block that folded this block's norm into its product")
+        if isinstance(delta, ScaledSum):
+            self.rt.ops.add_scaled_into_residual(resid, delta.rows, delta.factor)
+            delta = None
+        n1 = self.norm1.add_forward(resid, delta)
+        left = self._left_to_add(self.post_norm1, self.mixer.forward(n1, batch, cache, write_cache), resid)
+        if self.ffn is None:
+            return resid, left
+        n2 = self.norm2.add_forward(resid, left)
+        return resid, self._left_to_add(self.post_norm2, self.ffn.forward(n2, batch), resid)
+
+    def _left_to_add(self, norm, y, resid):
+        """norm(y) as something the next norm adds in its own pass, where both sides can; else it is added here."""
+        if hasattr(norm, "normed_sum") and os.environ.get("KIRAI_FUSE_NORMS", "1") != "0":
+            return norm.normed_sum(y)
+        norm.add_normed(resid, y)
+        return None
 
     def _forward_scaled(self, resid, delta, batch, cache, write_cache):
         """pre_norm with a factor on what the sub-layers add; their outputs are 32-bit rows."""

@@ -34,6 +34,13 @@ the framework's gated-activation kernel on its rows.  ``scoring="softmax_all"``:
 shares of the softmax over ALL experts' logits, not renormalised (the choice is the same: the largest logits).
 ``shared``: a feed-forward that runs for every token beside the routed experts; its output is added (``forward_terms``
 hands both terms to whoever adds them into the stream).
+
+``activation="clamped_gated"`` (with ``limit`` L and ``slope`` a): an expert is down(g sigmoid(a g) (u + 1)) with
+g = min(gate x, L) and u = clamp(up x, -L, L); laid out and run like ``silu_gated``.  ``scoring="sigmoid"``: an
+expert's score is sigmoid(z).  The choice looks at score + ``correction`` (a stored vector [experts], named by
+``names["correction"]``; None: no correction), and, with ``groups`` = (count, keep), only at experts of the ``keep``
+groups (of ``count`` equal groups of neighbouring experts) whose two largest choice scores sum highest.  The weights
+are the chosen experts' scores without the correction, not renormalised.
 """
 from __future__ import annotations
 
@@ -44,8 +51,8 @@ import torch
 from .base import FeedForward, Runtime, WeightSpec
 from .linear import Linear
 
-ACTIVATIONS = ("relu2", "silu_gated")
-SCORINGS = ("softmax_chosen", "softmax_all")
+ACTIVATIONS = ("relu2", "silu_gated", "clamped_gated")
+SCORINGS = ("softmax_chosen", "softmax_all", "sigmoid")
 GROUPED_MIN_ROWS = 512  # pairs of (token, chosen expert) from which a step sorts them by expert
 
 
@@ -55,19 +62,35 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, prefix: str, hidden_size: int, expert_size: int, experts: int, top: int, *,
                  activation: str = "relu2", names: Optional[Dict[str, str]] = None,
-                 out_dtype: Optional[torch.dtype] = None, scoring: str = "softmax_chosen", shared: Optional[FeedForward] = None):
+                 out_dtype: Optional[torch.dtype] = None, scoring: str = "softmax_chosen", shared: Optional[FeedForward] = None,
+                 limit: Optional[float] = None, slope: float = 1.0, correction: bool = False, groups: Optional[tuple] = None):
         if activation not in ACTIVATIONS:
             raise ValueError(f"unknown expert activation {activation!r}; known: {ACTIVATIONS}")
         if scoring not in SCORINGS:
             raise ValueError(f"unknown router scoring {scoring!r}; known: {SCORINGS}")
-        self.gated = activation == "silu_gated"
+        self.gated = activation in ("silu_gated", "clamped_gated")
+        self.gate_act = "clamped" if activation == "clamped_gated" else "silu"
+        if (activation == "clamped_gated") != (limit is not None) or (limit is not None and not limit > 0.0):
+            raise ValueError("the clamped activation, and it alone, takes a positive limit")
+        self.limit, self.slope = float(limit or 0.0), float(slope)
         self.over_all = scoring == "softmax_all"
+        self.scored = scoring == "sigmoid"
+        if (correction or groups is not None) and not self.scored:
+            raise ValueError("a correction on the choice and a choice among groups go with sigmoid scores")
+        count, keep = groups if groups is not None else (1, 1)
+        if experts % count or not 0 < keep <= count or top > keep * (experts // count):
+            raise ValueError(f"{experts} experts in {count} equal groups of which {keep} stay open do not give {top} experts a token")
+        self.groups = (int(count), int(keep))
+        self.has_correction = bool(correction)
+        self.correction: Optional[torch.Tensor] = None
+        self.rule: Optional[dict] = None
         self.shared = shared
         if not 0 < top <= experts:
             raise ValueError(f"every token uses {top} of {experts} experts")
         n = {"router": "router.weight", "up": "experts.{e}.up_proj.weight", "down": "experts.{e}.down_proj.weight",
-             "gate": "experts.{e}.gate_proj.weight"}
+             "gate": "experts.{e}.gate_proj.weight", "correction": "router.correction"}
         n.update(names or {})
+        self.correction_name = prefix + n["correction"]
         self.hidden_size, self.expert_size, self.experts, self.top = hidden_size, expert_size, experts, top
         self.activation = activation
         self.out_dtype = out_dtype
@@ -87,7 +110,8 @@ class RoutedExperts(FeedForward):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         shared = self.shared.weight_specs() if self.shared is not None else {}
-        return {self.router_name: WeightSpec((self.experts, self.hidden_size), "linear"),
+        correction = {self.correction_name: WeightSpec((self.experts,), "bias")} if self.has_correction else {}
+        return {self.router_name: WeightSpec((self.experts, self.hidden_size), "linear"), **correction,
                 **self.up.weight_specs(), **self.down.weight_specs(), **shared}
 
     @property
@@ -101,6 +125,10 @@ class RoutedExperts(FeedForward):
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
         self.router = weights.on_device(self.router_name, torch.float32)
+        if self.has_correction:
+            self.correction = weights.on_device(self.correction_name, torch.float32)
+        if self.scored:
+            self.rule = {"correction": self.correction, "groups": self.groups[0], "keep": self.groups[1]}
         self.up.load(weights, rt)
         self.down.load(weights, rt)
         if self.shared is not None:
@@ -121,8 +149,9 @@ class RoutedExperts(FeedForward):
     def _route(self, x: torch.Tensor, want_chosen: bool):
         ops = self.rt.ops
         if self.router_product is not None and x.shape[0] >= self.ROUTER_PRODUCT_MIN_ROWS:
-            return ops.router_choose_(self.router_product.forward(x, torch.float32), self.top, want_chosen, over_all=self.over_all)
-        return ops.router_gates(x, self.router, self.top, want_chosen, over_all=self.over_all)
+            return ops.router_choose_(self.router_product.forward(x, torch.float32), self.top, want_chosen, over_all=self.over_all,
+                                      rule=self.rule)
+        return ops.router_gates(x, self.router, self.top, want_chosen, over_all=self.over_all, rule=self.rule)
 
     def _sorts(self, rows: int) -> bool:
         return self.grouped and rows * self.top >= GROUPED_MIN_ROWS
@@ -134,7 +163,8 @@ class RoutedExperts(FeedForward):
         tile_group, slot_of, row_of_slot = ops.route_plan(ids, self.experts)
         rows = ops.route_gather(x, row_of_slot)
         if self.gated:
-            hidden = ops.gated_activation(ops.linear_grouped(rows, self.up.weight, self.experts, tile_group), "silu")
+            hidden = ops.gated_activation(ops.linear_grouped(rows, self.up.weight, self.experts, tile_group), self.gate_act,
+                                          self.limit, self.slope)
         else:
             hidden = ops.linear_grouped(rows, self.up.weight, self.experts, tile_group, relu2=True)
         return ops.linear_grouped(hidden, self.down_stacked.weight, self.experts, tile_group), slot_of, mix
@@ -171,7 +201,7 @@ class RoutedExperts(FeedForward):
         gates = self._route(x, False)
         hidden = self.up.forward(x)
         if self.gated:
-            hidden = ops.gated_expert_gate(hidden, gates, self.expert_size, "silu")
+            hidden = ops.gated_expert_gate(hidden, gates, self.expert_size, self.gate_act, self.limit, self.slope)
         else:
             ops.relu2_gate_(hidden, gates, self.expert_size)
         return self.down.forward(hidden, self.out_dtype)

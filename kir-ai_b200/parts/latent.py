@@ -15,6 +15,14 @@ and whose value row is c, on the framework's attention kernels (cache rows are k
 8; the value row repeats c).  Against attention over per-head keys and values this reads kv_rank + rot_dim columns
 a key instead of heads * (dim + rot_dim + vdim), and multiplies with queries of kv_rank + rot_dim columns instead
 of dim + rot_dim.
+
+With ``gate`` (the name of a matrix [heads * value_dim, hidden]) the concatenated heads' values are multiplied by
+sigmoid(gate x) ahead of the output projection.  A gate stands between W_uv and W_o, so W_uv is then NOT folded into
+the output projection: the attention's sums of latents go through a product per head (``ops.head_linear_gate``, the
+gate in the same kernel) and W_o reads heads * value_dim columns as stored; the gate's matrix rides in the stacked down
+projection.  A rotation that pairs neighbouring columns (``RotaryEmbedding(pairing="neighbours")``) has the rows that
+make the rotated query columns and the shared key part put in its ``head_order`` at load; a rotation with an
+``amplitude`` is applied with it by both preparation kernels.
 """
 from __future__ import annotations
 
@@ -32,9 +40,10 @@ class LatentAttention(Mixer):
 
     def __init__(self, prefix: str, hidden_size: int, heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int,
                  kv_rank: int, scale: float, eps: float, rotary: RotaryEmbedding, names: Optional[Dict[str, str]] = None,
-                 out_dtype: Optional[torch.dtype] = None):
+                 out_dtype: Optional[torch.dtype] = None, gate: Optional[str] = None):
         n = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o"}
         n.update(names or {})
+        self.gate_name = prefix + gate if gate else None
         if rotary.head_dim != rot_dim or rotary.rotary_dim != rot_dim or rotary.offset != 0:
             raise ValueError("the rotation of latent attention covers the whole shared key part")
         self.hidden_size, self.heads, self.dim, self.rot_dim, self.value_dim = hidden_size, heads, dim, rot_dim, value_dim
@@ -42,9 +51,21 @@ class LatentAttention(Mixer):
         self.row = kv_rank + rot_dim                 # a cached key row, and a query head in the latent's space
         self.pad_dim = -(-self.row // 8) * 8
         self.names = {key: prefix + value for key, value in n.items()}
-        self.down = Linear([(self.names["dq"], q_rank), (self.names["dkv"], kv_rank + rot_dim)], hidden_size)
+        self.order = rotary.head_order()  # of the rotated columns, where the rotation pairs neighbours
+        sources = [(self.names["dq"], q_rank), (self.names["dkv"], kv_rank + rot_dim)]
+        if self.gate_name:
+            sources.append((self.gate_name, heads * value_dim))
+        stacked_order = None
+        if self.order is not None:
+            stacked_order = torch.arange(sum(rows for _, rows in sources))
+            stacked_order[q_rank + kv_rank : q_rank + kv_rank + rot_dim] = q_rank + kv_rank + self.order
+        self.down = Linear(sources, hidden_size, row_order=stacked_order)
         self.up_q = Linear([("", heads * self.row)], q_rank)                 # filled from uq and uk at load
-        self.out = Linear([("", hidden_size)], heads * self.pad_dim)         # filled from o and uv at load
+        if self.gate_name:
+            self.out = Linear([(self.names["o"], hidden_size)], heads * value_dim)
+        else:
+            self.out = Linear([("", hidden_size)], heads * self.pad_dim)     # filled from o and uv at load
+        self.up_v: Optional[torch.Tensor] = None                             # [heads, value_dim, kv_rank], with a gate
         self.q_norm = self.kv_norm = None
 
     def cache_need(self) -> KVCacheNeed:
@@ -56,7 +77,7 @@ class LatentAttention(Mixer):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         n = self.names
-        return {**self.down.weight_specs(),
+        return {**self.down.weight_specs(), **(self.out.weight_specs() if self.gate_name else {}),
                 n["dq_norm"]: WeightSpec((self.q_rank,), "norm"), n["dkv_norm"]: WeightSpec((self.kv_rank,), "norm"),
                 n["uq"]: WeightSpec((self.heads * (self.dim + self.rot_dim), self.q_rank)),
                 n["uk"]: WeightSpec((self.heads * self.dim, self.kv_rank)),
@@ -76,8 +97,14 @@ class LatentAttention(Mixer):
         uv = weights.stored(n["uv"]).to(**wide).view(H, dv, kr)
         o = weights.stored(n["o"]).to(**wide).view(self.hidden_size, H, dv)
         # query head i in the latent's space: [W_uk,i^T W_uq,i (kv_rank rows); the rotated rows of W_uq,i]
-        up_q = torch.cat([torch.einsum("hdk,hdq->hkq", uk, uq[:, :d]), uq[:, d:]], dim=1)
+        rotated = uq[:, d:] if self.order is None else uq[:, d:][:, self.order.to(rt.device)]
+        up_q = torch.cat([torch.einsum("hdk,hdq->hkq", uk, uq[:, :d]), rotated], dim=1)
         self.up_q.load_matrix(up_q.reshape(H * self.row, self.q_rank), rt)
+        if self.gate_name:
+            # the gate stands between W_uv and W_o: both stay as stored
+            self.up_v = weights.stored(n["uv"]).to(device=rt.device, dtype=rt.dtype).view(H, dv, kr).contiguous()
+            self.out.load(weights, rt)
+            return
         # the output projection reads the heads' sums of latents: columns W_o,i W_uv,i, zero where a row is padding
         out = torch.zeros((self.hidden_size, H, self.pad_dim), **wide)
         out[:, :, :kr] = torch.einsum("ehv,hvk->ehk", o, uv)
@@ -89,11 +116,15 @@ class LatentAttention(Mixer):
         ops = self.rt.ops
         table = batch.block_tables[cache.group]
         down = self.down.forward(x, torch.float32)
+        amplitude = self.rotary.amplitude
         q_latent = ops.latent_prepare(down, self.q_rank, self.kv_rank, self.rot_dim, self.q_norm, self.kv_norm,
                                       self.rotary.inv_freq, self.eps, cache.kv, table, batch.request_of_token,
-                                      batch.positions, self.rt.dtype)
+                                      batch.positions, self.rt.dtype, rot_amplitude=amplitude)
         q = ops.qkv_rope_write(self.up_q.forward(q_latent, torch.float32), self.heads, 0, self.row, self.row, self.pad_dim,
                                None, None, None, None, self.rotary.inv_freq, self.kv_rank, self.rot_dim, None, table,
-                               batch.request_of_token, batch.positions, self.rt.dtype)
+                               batch.request_of_token, batch.positions, self.rt.dtype, rot_amplitude=amplitude)
         mixed = ops.paged_attention(q, cache.kv, table, batch, None, self.scale)
+        if self.gate_name:
+            gate = down[:, self.q_rank + self.kv_rank + self.rot_dim :]
+            mixed = ops.head_linear_gate(mixed.view(mixed.shape[0], -1), self.up_v, self.heads, self.kv_rank, gate)
         return self.out.forward(mixed, self.out_dtype)

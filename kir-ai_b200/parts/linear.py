@@ -20,13 +20,16 @@ class Linear(Part):
     kernels_only = True
 
     def __init__(self, sources: Sequence[Tuple[str, int]], in_features: int, *, side_by_side: bool = False,
-                 column_groups: Optional[Tuple[int, int, int]] = None):
+                 column_groups: Optional[Tuple[int, int, int]] = None, row_order: Optional[torch.Tensor] = None):
         """``side_by_side``: the sources [out, in_i] share the output axis and are laid next to each other along the
         input axis (``in_features`` is then the common OUTPUT size and the numbers in ``sources`` are input sizes), so
         that one product sums what each matrix makes of its share of the input columns.  ``column_groups`` =
         (groups, used, padded): the input arrives as ``groups`` groups of ``padded`` columns of which the first
         ``used`` are real (heads whose rows are narrower than the cache's); the stored matrix [out, groups * used]
-        gets zero columns at load."""
+        gets zero columns at load.  ``row_order`` [out_features]: the stacked rows are taken in this order (output column
+        j is stored row ``row_order[j]``), for a consumer that wants a projection's columns in another order than the
+        stored one."""
+        self.row_order = row_order
         self.sources: List[Tuple[str, int]] = list(sources)
         self.side_by_side = side_by_side
         self.column_groups = column_groups
@@ -35,6 +38,8 @@ class Linear(Part):
             self.out_features, self.in_features = in_features, total
         else:
             self.out_features, self.in_features = total, in_features
+        if row_order is not None and (side_by_side or row_order.numel() != self.out_features):
+            raise ValueError(f"a row order of {row_order.numel()} entries does not fit {self.out_features} stacked rows")
         if column_groups is not None:
             groups, used, padded = column_groups
             if side_by_side or groups * used != in_features or padded < used:
@@ -52,6 +57,8 @@ class Linear(Part):
         self.rt = rt
         parts = [weights.stored(name).to(device=rt.device, dtype=rt.dtype) for name, _ in self.sources]
         stacked = parts[0].contiguous() if len(parts) == 1 else torch.cat(parts, dim=1 if self.side_by_side else 0).contiguous()
+        if self.row_order is not None:
+            stacked = stacked[self.row_order.to(stacked.device)].contiguous()
         if self.column_groups is not None and self.column_groups[1] != self.column_groups[2]:
             groups, used, padded = self.column_groups
             wide = torch.zeros((stacked.shape[0], groups, padded), dtype=stacked.dtype, device=stacked.device)

@@ -11,27 +11,37 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import FusedNormSpec, Norm, Runtime, ScaledSum, WeightSpec
+from .base import FusedNormSpec, Norm, NormedSum, Runtime, ScaledSum, WeightSpec
 
 
 class RMSNorm(Norm):
     capture_safe = True
     kernels_only = True
 
-    def __init__(self, weight_name: str, width: int, eps: float):
+    def __init__(self, weight_name: str, width: int, eps: float, centre: float = 0.0):
+        """``centre`` c: the stored tensor w is the weight's distance from c, y = x / rms(x) * (c + w); a weight stored
+        around zero has c = 1.  The sum is formed once, in 32-bit, at load."""
         self.weight_name = weight_name
         self.width = width
         self.eps = float(eps)
+        self.centre = float(centre)
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {self.weight_name: WeightSpec((self.width,), "norm")}
+        return {self.weight_name: WeightSpec((self.width,), "bias" if self.centre else "norm")}
 
     def load(self, weights, rt: Runtime) -> None:
         self.rt = rt
         self.weight = weights.on_device(self.weight_name, torch.float32)
+        if self.centre:
+            self.weight = (self.weight + self.centre).contiguous()
 
-    def add_forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    takes_normed_sum = True  # add_forward and add_forward_rows take a ``NormedSum`` (base.py)
+
+    def add_forward(self, resid: torch.Tensor, delta) -> torch.Tensor:
+        if isinstance(delta, NormedSum):
+            # the stream takes the sub-layer's normed output and leaves under this norm in one pass over the row
+            return self.rt.ops.norm_add_norm(resid, delta.rows, delta.weight, delta.eps, self.weight, self.eps, self.rt.dtype)
         return self.rt.ops.add_rmsnorm(resid, delta, self.weight, self.eps, self.rt.dtype)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -51,8 +61,16 @@ class RMSNorm(Norm):
 
     def add_forward_rows(self, resid: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         """The norm of ``resid[rows] + delta[rows]`` only; the stream is left untouched."""
+        if isinstance(delta, NormedSum):
+            return self.rt.ops.norm_add_norm(resid, delta.rows, delta.weight, delta.eps, self.weight, self.eps, self.rt.dtype,
+                                             row_index=rows)
         out, _ = self.rt.ops.add_rmsnorm(resid, delta, self.weight, self.eps, self.rt.dtype, row_index=rows)
         return out
+
+    def normed_sum(self, y: torch.Tensor) -> "NormedSum":
+        """What is left to add when this norm stands on a sub-layer's OUTPUT ``y`` (32-bit rows) and whoever reads the
+        stream next adds it."""
+        return NormedSum(y if y.dtype == torch.float32 else y.float(), self.weight, self.eps)
 
 
 class LayerNorm(Norm):

@@ -17,6 +17,13 @@ wavelength makes t turns over ``original`` positions, lo = max(floor(dim(fast)),
 rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency becomes
 f_i / factor * ramp_i + f_i * (1 - ramp_i), and cosine and sine are multiplied by ``amplitude`` = 0.1 ln(factor) + 1
 (the attention preparation kernel takes that factor; ``apply`` alone does not rotate with it).
+
+``pairing="neighbours"`` pairs column 2i with column 2i + 1 (the interleaved layout) where the default, ``"halves"``,
+pairs column i with column i + rotary_dim / 2.  A score is a sum over columns, so it does not change when the columns
+of queries AND keys are put in another order: ``head_order()`` gives the order of a head's columns in which neighbours
+lie half a rotated part apart, a part that projects queries and keys applies it to the rows of its matrices (and
+biases) at load, and the kernels go on rotating halves.  Queries and keys of such a layer exist only in that order;
+values are left alone.
 """
 from __future__ import annotations
 
@@ -32,7 +39,10 @@ class RotaryEmbedding(PositionEncoding):
     kernels_only = True
 
     def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None, *, offset: int = 0,
-                 scaling: Optional[dict] = None, precise: bool = False):
+                 scaling: Optional[dict] = None, precise: bool = False, pairing: str = "halves"):
+        if pairing not in ("halves", "neighbours"):
+            raise ValueError(f"columns are paired as 'halves' or as 'neighbours', got {pairing!r}")
+        self.pairing = pairing
         self.head_dim = head_dim
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
         if self.rotary_dim % 2 or not 0 < self.rotary_dim or offset < 0 or offset + self.rotary_dim > head_dim:
@@ -92,7 +102,27 @@ class RotaryEmbedding(PositionEncoding):
         self.rt = rt
         self.inv_freq = self.frequencies().to(rt.device)
 
+    def head_order(self) -> Optional[torch.Tensor]:
+        """For ``pairing="neighbours"``: the stored columns of a head [head_dim] in the order in which the kernels want
+        them (the first of every pair, then the second of every pair, then the columns that are not rotated where they
+        were); None when the stored order is already the kernels'."""
+        if self.pairing == "halves":
+            return None
+        order = torch.arange(self.head_dim)
+        rotated = torch.arange(self.offset, self.offset + self.rotary_dim)
+        order[self.offset : self.offset + self.rotary_dim] = torch.cat([rotated[0::2], rotated[1::2]])
+        return order
+
+    def row_order(self, heads: int) -> Optional[torch.Tensor]:
+        """``head_order`` for the rows of a matrix [heads * head_dim, in] that projects ``heads`` heads."""
+        order = self.head_order()
+        if order is None:
+            return None
+        return (torch.arange(heads)[:, None] * self.head_dim + order[None, :]).reshape(-1)
+
     def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        if self.pairing != "halves":
+            raise ValueError("a rotation of neighbouring columns runs on projections whose rows were put in order at load")
         if self.amplitude != 1.0:
             raise ValueError("a rotation whose cosine and sine carry a factor runs inside the attention preparation only")
         if self.offset:

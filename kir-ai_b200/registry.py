@@ -76,6 +76,10 @@ def _register_builtin() -> None:
     from .models.figalix import build_figalix_plan
 
     register_architecture(FigalixConfig.architecture, FigalixConfig, build_figalix_plan, replace=True)
+    from .config.bikilix import BikilixConfig
+    from .models.bikilix import build_bikilix_plan
+
+    register_architecture(BikilixConfig.architecture, BikilixConfig, build_bikilix_plan, replace=True)
 
 
 _register_builtin()
