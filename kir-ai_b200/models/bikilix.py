@@ -1,7 +1,7 @@
 """The Bikilix decoder put together from parts.
 
 Embedding rows times a constant; layers with a norm before AND after each sub-layer, x <- x + norm1b(mixer(norm1(x))),
-x <- x + norm2b(ff(norm2(x))), every norm an RMS norm whose weight is stored around zero (y = x / rms(x) * (1 + w));
+x <- x + norm2b(ff(norm2(x))), every norm an RMS norm whose stored tensor is the weight minus one (y = x / rms(x) * (1 + w));
 two kinds of mixer, in whatever order the configuration lists them: grouped-query attention with biases on q, k and v,
 a rotated leading part of every head (neighbouring columns paired) and a sliding window, and latent attention (one
 small cached row per token for all heads, queries through a latent of their own, the shared key part rotated with

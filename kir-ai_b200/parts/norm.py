@@ -19,8 +19,8 @@ class RMSNorm(Norm):
     kernels_only = True
 
     def __init__(self, weight_name: str, width: int, eps: float, centre: float = 0.0):
-        """``centre`` c: the stored tensor w is the weight's distance from c, y = x / rms(x) * (c + w); a weight stored
-        around zero has c = 1.  The sum is formed once, in 32-bit, at load."""
+        """``centre`` c: the stored tensor w is the weight's distance from c, y = x / rms(x) * (c + w); a tensor that holds
+        the weight minus one has c = 1.  The sum is formed once, in 32-bit, at load."""
         self.weight_name = weight_name
         self.width = width
         self.eps = float(eps)

@@ -13,7 +13,7 @@ F = torch.float64
 
 
 def unit_norm(x, w, eps, centre=0.0):
-    """x / sqrt(mean(x^2) + eps) * (centre + w) over the last axis: ``centre`` 1 for a weight stored around zero."""
+    """x / sqrt(mean(x^2) + eps) * (centre + w) over the last axis: ``centre`` 1 when the tensor holds the weight minus one."""
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * (centre + w)
 
 
@@ -62,7 +62,8 @@ def softmax_rows(scores, visible):
 
 
 def window_attention(n, w, m, prefix, probabilities=None):
-    """Grouped-query attention with biases on q, k, v, a rotated leading part of every head and a sliding window."""
+    """Grouped-query attention with biases on q, k, v, a rotated leading part of every head and a sliding window
+    (position i sees j when 0 <= i - j < size)."""
     T = n.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     positions = torch.arange(T)
@@ -71,7 +72,9 @@ def window_attention(n, w, m, prefix, probabilities=None):
     v = (n @ w[prefix + "v"].T + w[prefix + "v.b"]).view(T, G, dv)
     q, k = rotate_neighbours(q, positions, m["rot"]), rotate_neighbours(k, positions, m["rot"])
     i, j = positions[:, None], positions[None, :]
-    visible = (j <= i) & (i - j < m["mask"]["size"])
+    visible = j <= i
+    if m.get("mask"):
+        visible = visible & (i - j < m["mask"]["size"])
     per = H // G
     heads = []
     for h in range(H):
@@ -120,7 +123,8 @@ def router_choice(n, w, mlp, prefix, margins=None):
     score + correction, only inside the ``keep`` groups whose two largest such numbers sum highest; the weights are the
     scores themselves.  ``margins`` collects, per token, the smallest gap that decided a choice."""
     router = mlp["router"]
-    E, top, groups, keep = router["experts"], router["top"], router["groups"]["count"], router["groups"]["keep"]
+    E, top = router["experts"], router["top"]
+    groups, keep = (router["groups"]["count"], router["groups"]["keep"]) if router.get("groups") else (1, 1)
     score = torch.sigmoid(n @ w[prefix + "router"].T)
     choice = score + w[prefix + "correction"]
     T = n.shape[0]
