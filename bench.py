@@ -305,6 +305,32 @@ def figalix_config(size: dict, layers: int, intermediate: int) -> dict:
             "layers": [{"type": mixers[i % 2][0], "mixer": dict(mixers[i % 2][1]), "mlp": dict(mlps[i % 2])} for i in range(layers)]}
 
 
+BIKILIX_LATENT = dict(heads=16, dim=64, rot_dim=64, vdim=64, kv_rank=192)  # a cached row of 256 columns a token
+BIKILIX_WINDOW = 1024
+
+
+def bikilix_config(size: dict, layers: int, intermediate: int) -> dict:
+    """A Bikilix config.json of one size: layers in the order latent attention, latent attention, attention, attention
+    (and so on); latent attention with 16 heads over a cached row of 256 columns, its rotated part stretched by index;
+    attention with the size's heads, a quarter of each head rotated, a window of 1,024; the first layer of four with a
+    dense relu^2 feed-forward that holds as many weights as the dense model's gated one, the others with the size's
+    experts (clamped gate, two of four groups open); all layers are one pass of a loop, so that the stream is merged
+    with the embedding's rows once."""
+    width = size["width"]
+    attention = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["dim"], "vdim": size["vdim"],
+                 "scale": size["dim"] ** -0.5, "mask": {"size": BIKILIX_WINDOW}, "rot": {"base": 1000000.0, "dims": size["dim"] // 4}}
+    lat = dict(BIKILIX_LATENT, q_rank=width // 4 + width // 8, scale=(BIKILIX_LATENT["dim"] + BIKILIX_LATENT["rot_dim"]) ** -0.5,
+               rot={"base": 500000.0, "dims": BIKILIX_LATENT["rot_dim"],
+                    "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}})
+    mixers = [("latent_attention", lat), ("latent_attention", lat), ("attention", attention), ("attention", attention)]
+    experts = {"kind": "moe", "expert": {"ff": size["ff"], "limit": 7.0},
+               "router": {"experts": size["experts"], "top": size["top"], "groups": {"count": 4, "keep": 2}}}
+    mlps = [{"kind": "dense", "ff": 3 * intermediate // 2}, experts, experts, experts]
+    return {"architecture": "Bikilix", "width": width, "vocab": size["vocab"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": [{"type": mixers[i % 4][0], "mixer": dict(mixers[i % 4][1]), "mlp": dict(mlps[i % 4])} for i in range(layers)],
+            "loop": {"start": 0, "stop": layers, "times": 1}}
+
+
 def design_configs(size: dict, layers: int):
     """(Zoferax config.json, Qwen3 config.json, Silupel config.json) of one size: the same width, heads and layer count;
     the dense feed-forward is as large as the experts that one token uses (3 I H = 2 top ff H)."""
@@ -318,7 +344,7 @@ def design_configs(size: dict, layers: int):
                  head_dim=size["dim"], vocab_size=size["vocab"], max_position_embeddings=40960, rms_norm_eps=1e-6,
                  rope_theta=1000000.0, tie_word_embeddings=False)
     return {"zoferax": zoferax, "qwen3-dense": dense, "silupel": silupel_config(size, layers, intermediate),
-            "figalix": figalix_config(size, layers, intermediate)}
+            "figalix": figalix_config(size, layers, intermediate), "bikilix": bikilix_config(size, layers, intermediate)}
 
 
 def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: float, size: dict, design: str, peaks,
@@ -329,7 +355,7 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
     import re
 
     width, heads, kvh, dk = size["width"], size["heads"], size["kv_heads"], size["dim"]
-    dv = size["vdim"] if design in ("zoferax", "silupel", "figalix") else dk
+    dv = size["vdim"] if design in ("zoferax", "silupel", "figalix", "bikilix") else dk
     visible = visible or (lambda mask: (context_pairs, cache_rows))
     routed = size["experts"] * size["ff"]
     rows = []
@@ -347,7 +373,7 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
         elif match:
             m, n, k, form = map(int, match.groups())
             flops, bytes_ = 2.0 * m * n * k, 2.0 * (m * k + n * k) + m * (n // 2 if form == 2 else n) * (4 if form in (1, 3) else 2)
-            if design == "zoferax" and routed in (n, k):  # the experts: a token needs top of them
+            if design in ("zoferax", "bikilix") and (routed in (n, k) or 2 * routed == n):  # the experts: a token needs top of them
                 share = size["top"] / size["experts"]
                 flops *= share
                 bytes_ = 2.0 * m * k * (share if k == routed else 1) + 2.0 * n * k * min(1.0, share * max(1, m)) + m * n * 2.0 * (share if n == routed else 2)
@@ -357,12 +383,23 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
             # a launch that says its shape: pairs and cache rows of the keys that its mask lets a query see
             a_heads, a_kv, a_d, a_mask = (int(v) for v in re.search(r"heads=(\d+) kv=(\d+) d=(\d+) mask=(-?\d+)", name).groups())
             pairs, rows_read = visible(a_mask)
-            shared = 1.0 if (design == "silupel" and a_kv == 1) else 2.0  # a latent row is key and value in one
+            shared = 1.0 if (design in ("silupel", "bikilix") and a_kv == 1) else 2.0  # a latent row is key and value in one
             flops = 2.0 * a_heads * 2 * a_d * pairs * count
             bytes_ = (2.0 * a_kv * shared * a_d * rows_read + 2.0 * tokens * a_heads * 2 * a_d) * count
         elif "attention" in name:
             flops = 2.0 * heads * (dk + dv) * context_pairs * count
             bytes_ = (2.0 * kvh * (dk + dv) * cache_rows + 2.0 * tokens * heads * (dk + dv)) * count
+        elif "head_linear_gate" in name:
+            # a product per head between the attention over the shared latent and the output projection, and the gate
+            t_, h_, k_, n_ = (int(v) for v in re.search(r"t=(\d+) heads=(\d+) k=(\d+) n=(\d+)", name).groups())
+            flops = 2.0 * t_ * h_ * k_ * n_ * count
+            bytes_ = (2.0 * t_ * h_ * (k_ + n_) + 4.0 * t_ * h_ * n_ + 2.0 * h_ * k_ * n_) * count
+        elif "norm_add_norm" in name:
+            bytes_ = tokens * width * 14.0 * count
+        elif "stream_copy" in name:
+            bytes_ = tokens * width * 6.0 * count
+        elif "kirai_relu2_" in name and "gate" not in name:
+            bytes_ = tokens * size.get("intermediate", width) * 3 // 2 * 4.0 * count
         elif "ssm_walk" in name or "matrix_memory_walk" in name:
             # a walk: every token touches the whole state of every head once (decay, outer product, read-out), in 32-bit
             # on the ordinary pipe; a request's state is read and written once a step
@@ -573,7 +610,7 @@ def main() -> int:
                              "equal layer sizes (--sizes), with every step's time by kernel; a line of its own.")
     parser.add_argument("--sizes", default="2k,4k", help="layer sizes of --workload designs: " + ", ".join(DESIGN_SIZES))
     parser.add_argument("--designs", default="zoferax,qwen3-dense",
-                        help="which designs --workload designs measures, comma separated: zoferax, silupel, figalix, qwen3-dense")
+                        help="which designs --workload designs measures, comma separated: zoferax, silupel, figalix, bikilix, qwen3-dense")
     args = parser.parse_args()
 
     if args.impl == "reference":

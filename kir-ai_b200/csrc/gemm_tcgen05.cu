@@ -98,7 +98,7 @@ __host__ __device__ constexpr int tmem_columns() { return BN <= 32 ? 32 : (BN <=
 //    (0 when that variance is 0), which is what the product of the normed rows would have been.
 //  * EPI 2 (residual and next norm): residual[m][n] += product; C[m][n] = bf16(residual * norm_weight[n]) is the
 //    unscaled input of the next product, and sumsq_out[tile][m] receives this tile's share of sum_n residual^2.
-//  * EPI 3 (persistent kernel only): C = relu(product)^2.
+//  * EPI 3: C = relu(product)^2.
 struct Epilogue {
     const float* row_sumsq;
     int row_parts;
@@ -465,6 +465,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             if (ep.row_sumsq) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] *= SWAP ? scale_s[c0 + j] : my_scale;
+            }
+            if (EPI == 3) {
+                // (v holds the whole sum over K here, also where the cluster split it)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = v[j] > 0.0f ? v[j] * v[j] : 0.0f;
             }
             if (tile_row == 0) gemm_stamp(ep, 6);
             if (SWAP && staged) {
@@ -1265,7 +1270,8 @@ KIRAI_EXPORT int kirai_gemm_bf16_grouped(const void* A, const void* W, int tiled
 // The one entry point of the tensor-core product, A[M, K] (row stride lda) times W[N, K] transposed.
 //   tiled:  W is in the tiled form described at the top of this file, else row-major.
 //   form 0: C[M, N] bf16.  1: C[M, N] float.  2: C[M, N / 2] = silu(gate) * up, W's rows in groups of 8 gate rows
-//           followed by their 8 up rows.  5: as 2 with the tanh form of gelu in place of silu.  3: residual[M, N] (float, in place) += product, C[M, N] =
+//           followed by their 8 up rows.  5: as 2 with the tanh form of gelu in place of silu.  4: C[M, N] bf16 =
+//           relu(product)^2.  3: residual[M, N] (float, in place) += product, C[M, N] =
 //           bf16(residual * norm_weight[n]) and sumsq_out[parts][M] = each column tile's share of sum_n residual^2.
 //   row_sumsq (forms 0-2, may be null): the rows of A were left unscaled by an RMSNorm; row m of the product is
 //           multiplied by 1 / sqrt(sum_p row_sumsq[p][m] / row_count + row_eps).
@@ -1284,6 +1290,7 @@ KIRAI_EXPORT int kirai_gemm_bf16_general(const void* A, const void* W, int tiled
         case 5:
             ep.gate_act = 1;
             return gemm_dispatch<bf16, 1>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
+        case 4: return gemm_dispatch<bf16, 3>(A, W, tiled != 0, C, M, N, K, lda, ldc, splits, ep, error_flag, stream);
         case 3:
             if (!residual || !norm_weight || !sumsq_out || row_sumsq) return KIRAI_ERR_BAD_SIZE;
             ep.residual = residual, ep.norm_weight = norm_weight, ep.sumsq_out = sumsq_out;

@@ -1544,7 +1544,7 @@ def _gemm(x, weight, out, n: int, k: int, width: int, splits: int, form: int, ro
         sumsq = row_scale[0]
         assert sumsq.dtype == torch.float32 and sumsq.dim() == 2 and sumsq.shape[1] == x.shape[0] and sumsq.is_contiguous()
     item = (x, weight, out, n, k, width, splits, form, row_scale, resid, norm_weight, sumsq_out)
-    if chaining() and isinstance(weight, TiledWeight) and x.shape[0] <= 64 and splits == 0 and form != 5:
+    if chaining() and isinstance(weight, TiledWeight) and x.shape[0] <= 64 and splits == 0 and form not in (4, 5):
         if _pending and _pending[0][0].shape[0] != x.shape[0]:
             flush_products()
         _pending.append(item)
@@ -1570,7 +1570,7 @@ def _check_product(x, weight) -> tuple:
 
 def linear_tcgen05(x: torch.Tensor, weight, out_dtype: Optional[torch.dtype] = None,
                    splits: int = 0, swiglu: bool = False, row_scale: Optional[tuple] = None,
-                   gate_act: str = "silu") -> torch.Tensor:
+                   gate_act: str = "silu", relu2: bool = False) -> torch.Tensor:
     """bf16 ``x`` [M, K] times ``weight`` [N, K] transposed on the tcgen05 tensor cores (32-bit accumulation).
 
     ``weight`` is a row-major tensor or a ``TiledWeight``.  K and the row stride of ``x`` must be multiples of 8
@@ -1579,15 +1579,17 @@ def linear_tcgen05(x: torch.Tensor, weight, out_dtype: Optional[torch.dtype] = N
     and the result is silu(gate) * up, [M, N / 2] (``gate_act`` "gelu_tanh": the tanh form of gelu in place of silu).
     ``row_scale`` = (sumsq [P, M] float32, count, eps) multiplies
     row m of the product by 1 / sqrt(sum_p sumsq[p, m] / count + eps): ``x`` then holds rows that an RMSNorm left
-    unscaled.
+    unscaled.  ``relu2``: the result is relu(product)^2 (bfloat16).
     """
     m, k, n = _check_product(x, weight)
     out_dtype = out_dtype or torch.bfloat16
     if swiglu:
-        assert out_dtype == torch.bfloat16 and n % 16 == 0
+        assert out_dtype == torch.bfloat16 and n % 16 == 0 and not relu2
+    if relu2:
+        assert out_dtype == torch.bfloat16
     width = n // 2 if swiglu else n
     out = torch.empty((m, width), dtype=out_dtype, device=x.device)
-    form = (5 if gate_act == "gelu_tanh" else 2) if swiglu else (0 if out_dtype == torch.bfloat16 else 1)
+    form = (5 if gate_act == "gelu_tanh" else 2) if swiglu else (4 if relu2 else (0 if out_dtype == torch.bfloat16 else 1))
     assert gate_act in GATED_ACTIVATIONS
     _gemm(x, weight, out, n, k, width, splits, form, row_scale, None, None, None)
     return out
@@ -1607,6 +1609,17 @@ def linear_residual_norm(x: torch.Tensor, weight, resid: torch.Tensor, norm_weig
     sumsq = torch.empty((parts, m), dtype=torch.float32, device=x.device)
     _gemm(x, weight, rows, n, k, n, splits, 3, None, resid, norm_weight, sumsq)
     return rows, sumsq
+
+
+def linear_relu2_takes(x: torch.Tensor, weight) -> bool:
+    """Whether ``linear_relu2`` runs for these operands: the tensor-core product with the activation in its epilogue."""
+    n = weight.shape[0]
+    return tcgen05_takes(x) and n % 8 == 0 and (isinstance(weight, TiledWeight) or weight.dtype == torch.bfloat16)
+
+
+def linear_relu2(x: torch.Tensor, weight) -> torch.Tensor:
+    """relu(``x`` ``weight``^T)^2 in bfloat16, the activation in the product's epilogue."""
+    return linear_tcgen05(x, weight, torch.bfloat16, relu2=True)
 
 
 def tcgen05_takes(x: torch.Tensor) -> bool:

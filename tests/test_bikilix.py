@@ -86,8 +86,9 @@ TINY = {"A": (CONFIG_A, 4, 11), "B": (CONFIG_B, 8, 12)}  # name -> (config, page
 
 
 def write_model(folder, raw, seed, std=0.08):
-    """Random weights; the norms' stored tensors (around zero) and the routers' corrections are made larger than the
-    random-weights mode makes them, so that a lost ``1 +`` or a lost correction shows."""
+    """Random weights; the norms' stored tensors (the weights minus one) and the routers' corrections are made larger
+    than the random-weights mode makes them, so that a lost ``1 +`` or a lost correction shows and the experts' choice
+    scores lie far enough apart that few choices are close calls."""
     import kirai_b200  # noqa: F401
     from kirai_b200.registry import config_from_dict, plan_for_config
     from kirai_b200.weights.random_init import random_tensors
@@ -96,8 +97,10 @@ def write_model(folder, raw, seed, std=0.08):
     cfg = config_from_dict(raw)
     tensors = random_tensors(plan_for_config(cfg).weight_specs(), seed, std=std, norm_jitter=0.3, dtype=torch.bfloat16)
     for name in tensors:
-        if name.endswith(".correction") or ".norm" in name and not name.endswith((".dq.norm", ".dkv.norm")) or name == "loop.step":
+        if ".norm" in name and not name.endswith((".dq.norm", ".dkv.norm")) or name == "loop.step":
             tensors[name] = (tensors[name].float() * 4).to(torch.bfloat16)
+        if name.endswith(".correction"):
+            tensors[name] = (tensors[name].float() * 8 * 0.08 / std).to(torch.bfloat16)
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w", encoding="utf-8") as handle:
         json.dump(cfg.to_dict(), handle, indent=2)
@@ -107,7 +110,7 @@ def write_model(folder, raw, seed, std=0.08):
 def tolerance(dtype, reference):
     dtype = {torch.float32: "float32", torch.bfloat16: "bfloat16"}.get(dtype, dtype)
     peak = float(np.abs(np.asarray(reference)).max())
-    return 3e-5 * max(1.0, peak) if dtype == "float32" else 0.035 * peak
+    return 3e-5 * max(1.0, peak) if dtype == "float32" else 0.05 * peak
 
 
 def close(dtype, got, expected, what, rows=None):
@@ -476,24 +479,37 @@ def test_attention_parts_whole_in_portions_and_one_by_one(dtype, entry, width, p
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window,page", [(48, 16), (21, 16), (16, 16), (5, 8)])
 def test_keys_just_inside_and_just_outside_the_window_show(dtype, window, page):
-    """Row 20 is made thirty times larger than the rest.  With a window of W, queries 20 .. 20 + W - 1 see it (it
-    swamps them) and query 20 + W must not.  In a prompt portion that crosses the edge, in portions cut at the edge, and
-    decoded one by one; the windows end inside a page, on a page's border and span several pages."""
+    """Row 20 gets a component thirty times the size of a row that the key matrix cannot see (it lies in the matrix's
+    null space) and the value matrix can: its key is an ordinary key, its value swamps whoever attends to it.  Every
+    query head's matrix repeats the key matrix and the rows at the window's edge repeat row 20 as it was, so that
+    their queries equal that key up to the few rotated columns and give it a third of their weight.  With a window of
+    W, queries 20 .. 20 + W - 1 see row 20 and query 20 + W must not.  In a prompt portion that crosses the edge, in
+    portions cut at the edge, and decoded one by one; the windows end inside a page, on a page's border and span
+    several pages."""
     from part_helpers import Session, load_part
+    from kirai_b200.weights.random_init import random_tensors
 
-    entry = attn(8, 2, 64, 64, 0.8, rot(10000.0, 48), window)
-    part, raw = _mixer_part(entry, 128)
-    w = {k: v.double() for k, v in load_part(part, dtype, seed=9).items()}
-    x = torch.randn((90, 128), generator=torch.Generator().manual_seed(2)) * 1.5
-    x[20] *= 30
-    x = x.to(dtype)
-    expected = plain.window_attention(x.double(), w, raw["mixer"], "a.")
-    off_by_one = json.loads(json.dumps(raw["mixer"]))
+    part, raw = _mixer_part(attn(8, 1, 64, 64, 0.1, rot(10000.0, 8), window), 128)
+    tensors = random_tensors(part.weight_specs(), 9, std=0.08, norm_jitter=0.1, dtype=torch.bfloat16)
+    for head in range(8):
+        tensors["a.q"][64 * head : 64 * head + 64] = tensors["a.k"]
+        tensors["a.q.b"][64 * head : 64 * head + 64] = tensors["a.k.b"]
+    w = {k: v.double() for k, v in load_part(part, dtype, seed=9, tensors=tensors).items()}
     edge = 20 + window
+    x = torch.randn((90, 128), generator=torch.Generator().manual_seed(2)) * 1.5
+    x[edge - 1] = x[20]
+    x[edge] = x[20]
+    unseen = torch.linalg.svd(w["a.k"]).Vh[-1]  # W_k [64, 128] times this direction is zero
+    x[20] += (30 * 1.5 * 128 ** 0.5 * unseen).float()
+    x = x.to(dtype)
+    probabilities = []
+    expected = plain.window_attention(x.double(), w, raw["mixer"], "a.", probabilities)
+    assert float(probabilities[0][edge - 1, 20]) > 0.3
+    off_by_one = json.loads(json.dumps(raw["mixer"]))
     for size in (window - 1, window + 1):
         off_by_one["mask"]["size"] = size
         wrong = plain.window_attention(x.double(), w, off_by_one, "a.")
-        assert float((wrong - expected)[edge - 2 : edge + 2].abs().max()) > 20 * tolerance(dtype, expected.numpy())
+        assert float((wrong - expected)[edge - 2 : edge + 2].abs().max()) > 3 * tolerance(dtype, expected.numpy())
     session = Session([part.cache_need()], dtype, page_size=page, num_pages=2 * (-(-90 // page)), num_slots=2)
     for cuts in ([90], [edge - 1, 2, 90 - edge - 1], [edge, 90 - edge], [edge - 3] + [1] * (93 - edge), [20, 1, 69]):
         close(dtype, _run_part(part, session, x, cuts), expected, f"window {window}, cut as {cuts[:4]}...")
@@ -509,7 +525,7 @@ def test_a_far_key_that_stands_out_in_latent_attention(dtype):
     from part_helpers import Session, load_part
     from kirai_b200.weights.random_init import random_tensors
 
-    part, raw = _mixer_part(latent(4, 32, 16, 32, 48, 48, 0.8, scaling=(8.0, 64, 32.0, 1.0)), 96)
+    part, raw = _mixer_part(latent(4, 32, 4, 32, 48, 48, 0.8, scaling=(8.0, 64, 32.0, 1.0)), 96)
     tensors = random_tensors(part.weight_specs(), 21, std=0.08, norm_jitter=0.1, dtype=torch.bfloat16)
     tensors["a.dkv"][:48] = tensors["a.dq"]
     tensors["a.dkv.norm"] = tensors["a.dq.norm"].clone()
@@ -591,7 +607,7 @@ def tiny(request, tmp_path_factory):
 @pytest.mark.gpu
 def test_close_calls_are_few(tiny):
     for rid, reference in tiny["reference"].items():
-        assert reference.close.mean() <= 0.4, rid
+        assert reference.close.mean() <= 0.5, rid
 
 
 @pytest.mark.gpu
@@ -725,7 +741,7 @@ def test_long_prompts_whole_in_portions_and_beside_decoded_tokens(dtype, tmp_pat
     config, weights = read_model_folder(folder)
     long_a, long_b = random_tokens(650, 320, 1), random_tokens(420, 320, 2)
     ref_a, ref_b = reference_with_close_calls(config, weights, long_a), reference_with_close_calls(config, weights, long_b)
-    assert ref_a.close.mean() < 0.4 and ref_b.close.mean() < 0.4
+    assert ref_a.close.mean() < 0.5 and ref_b.close.mean() < 0.5
     replay = Replay(folder, dtype, str(tmp_path / "out"), max_tokens=1200, page_size=16)
     want = [0, 63, 64, 99, 100, 101, 163, 164, 199, 200, 399, 400, 511, 512, 600, 649]
     got = replay.step([("a", long_a, want)], end=["a"])
@@ -812,9 +828,14 @@ def test_random_configurations_whole_in_portions_and_mixed(seed, dtype, tmp_path
     config, weights = read_model_folder(folder)
     sequences = {rid: random_tokens(n, raw["vocab"], 300 + seed + k) for k, (rid, n) in enumerate([("a", 83), ("b", 37), ("c", 58)])}
     reference = {rid: reference_with_close_calls(config, weights, toks) for rid, toks in sequences.items()}
-    bound = {rid: (3e-5 * max(1.0, float(np.abs(ref).max())) if dtype == "float32" else 0.05 * float(np.abs(ref).max()))
+    bound = {rid: (3e-5 * max(1.0, float(np.abs(ref).max())) if dtype == "float32" else 0.07 * float(np.abs(ref).max()))
              for rid, ref in reference.items()}
     runner = ModelRunner.from_folder(folder, dtype=dtype, page_size=page, max_tokens=3 * 96, num_slots=4)
+    whole = {}  # every request alone and whole through the framework: what any other schedule must give, up to rounding
+    for rid, toks in sequences.items():
+        request = runner.cache.open((rid, "whole"))
+        whole[rid] = runner.step([StepEntry(request, toks, list(range(len(toks))))]).cpu().numpy()
+        runner.cache.close(request)
 
     def run(steps):
         live, done = {}, {rid: 0 for rid in sequences}
@@ -834,6 +855,10 @@ def test_random_configurations_whole_in_portions_and_mixed(seed, dtype, tmp_path
                 if dtype == "bfloat16":
                     diff = np.where(reference[rid].close[first : first + count], 0.0, diff)
                 assert float(diff.max()) <= bound[rid], f"{raw}: {rid} at {first}+{count}: max abs diff {float(diff.max())} (bound {bound[rid]})"
+                own = np.abs(logits[row : row + count] - whole[rid][first : first + count]).max(axis=1)
+                if dtype == "bfloat16":
+                    own = np.where(reference[rid].close[first : first + count], 0.0, own)
+                assert float(own.max()) <= 0.6 * bound[rid], f"{raw}: {rid} at {first}+{count} against its whole run: {float(own.max())}"
                 row += count
         for request in live.values():
             runner.cache.close(request)
