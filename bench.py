@@ -389,6 +389,9 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
         elif "attention" in name:
             flops = 2.0 * heads * (dk + dv) * context_pairs * count
             bytes_ = (2.0 * kvh * (dk + dv) * cache_rows + 2.0 * tokens * heads * (dk + dv)) * count
+        elif "head_major" in name or "head_gate_rows" in name:
+            bytes_ = tokens * BIKILIX_LATENT["heads"] * (4.0 * (BIKILIX_LATENT["kv_rank"] + BIKILIX_LATENT["rot_dim"]) if "major" in name
+                                                          else 10.0 * BIKILIX_LATENT["vdim"]) * count
         elif "head_linear_gate" in name:
             # a product per head between the attention over the shared latent and the output projection, and the gate
             t_, h_, k_, n_ = (int(v) for v in re.search(r"t=(\d+) heads=(\d+) k=(\d+) n=(\d+)", name).groups())
@@ -449,6 +452,8 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
             bytes_ = tokens * 6.0 * (heads * dk + kvh * (dk + dv)) * count
         elif "sigmoid_gate" in name:
             bytes_ = tokens * heads * dv * 8.0 * count
+        elif "gated_activation" in name and design == "bikilix":
+            bytes_ = tokens * size["top"] * size["ff"] * 6.0 * count  # the chosen experts' rows: gate and up in, hidden out
         elif "gated_activation" in name:
             bytes_ = tokens * size.get("intermediate", width) * 6.0 * count
         elif "norm_add" in name:

@@ -188,11 +188,83 @@ __global__ void norm_add_norm_kernel(float* __restrict__ resid, const float* __r
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>(row_s[i] * scale_next * w_next[i]);
 }
 
+// The same with 16-byte loads, the row kept in registers between the two statistics and the output (width a multiple
+// of 4, at most 4 * VEC * blockDim values).
+template <typename T, int VEC>
+__global__ void norm_add_norm_vec_kernel(float* __restrict__ resid, const float* __restrict__ y, const float* __restrict__ w_add,
+                                         const float* __restrict__ w_next, T* __restrict__ out, const int* __restrict__ row_index,
+                                         int hidden, float eps_add, float eps_next) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int row = row_index ? row_index[blockIdx.x] : (int)blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(y + (size_t)row * hidden);
+    float4* stream = reinterpret_cast<float4*>(resid + (size_t)row * hidden);
+    const float4* wa = reinterpret_cast<const float4*>(w_add);
+    const float4* wn = reinterpret_cast<const float4*>(w_next);
+    const int quads = hidden >> 2;
+    float4 kept[VEC], old[VEC];
+    float acc = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < quads) {
+            kept[n] = src[i];
+            old[n] = stream[i];
+            acc += (kept[n].x * kept[n].x + kept[n].y * kept[n].y) + (kept[n].z * kept[n].z + kept[n].w * kept[n].w);
+        }
+    }
+    const float var_add = block_sum(acc, scratch) / (float)hidden + eps_add;
+    const float scale_add = var_add == 0.0f ? 0.0f : 1.0f / sqrtf(var_add);
+    acc = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < quads) {
+            const float4 w = wa[i];
+            float4 r = old[n];
+            r.x += kept[n].x * scale_add * w.x, r.y += kept[n].y * scale_add * w.y;
+            r.z += kept[n].z * scale_add * w.z, r.w += kept[n].w * scale_add * w.w;
+            kept[n] = r;
+            if (!row_index) stream[i] = r;
+            acc += (r.x * r.x + r.y * r.y) + (r.z * r.z + r.w * r.w);
+        }
+    }
+    const float var_next = block_sum(acc, scratch) / (float)hidden + eps_next;
+    const float scale_next = var_next == 0.0f ? 0.0f : 1.0f / sqrtf(var_next);
+    T* dst = out + (size_t)blockIdx.x * hidden;
+#pragma unroll
+    for (int n = 0; n < VEC; ++n) {
+        const int i = threadIdx.x + n * blockDim.x;
+        if (i < quads) {
+            const float4 w = wn[i];
+            const float4 r = kept[n];
+            const float a = r.x * scale_next * w.x, b = r.y * scale_next * w.y, c = r.z * scale_next * w.z, d = r.w * scale_next * w.w;
+            if (sizeof(T) == 4) {
+                reinterpret_cast<float4*>(dst)[i] = make_float4(a, b, c, d);
+            } else {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(dst)[i] = packed;
+            }
+        }
+    }
+}
+
 template <typename T>
 static int norm_add_norm_launch(float* resid, const float* y, const float* w_add, const float* w_next, void* out,
                                 const int* row_index, int rows, int hidden, float eps_add, float eps_next, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0 || hidden > 12 * 1024) return KIRAI_ERR_BAD_SIZE;
+    const bool aligned = hidden % 4 == 0 &&
+                         (((uintptr_t)resid | (uintptr_t)y | (uintptr_t)w_add | (uintptr_t)w_next | (uintptr_t)out) & 15) == 0;
+    if (aligned && hidden <= 4 * 4 * 512) {
+        const int vec_threads = hidden <= 4 * 4 * 128 ? 128 : (hidden <= 4 * 4 * 256 ? 256 : 512);
+        return launch_pdl(norm_add_norm_vec_kernel<T, 4>, dim3(rows), dim3(vec_threads), 0, stream, 1u, resid, y, w_add, w_next, (T*)out,
+                          row_index, hidden, eps_add, eps_next);
+    }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     return launch_pdl(norm_add_norm_kernel<T>, dim3(rows), dim3(threads), (size_t)hidden * sizeof(float), stream, 1u, resid, y, w_add,
                       w_next, (T*)out, row_index, hidden, eps_add, eps_next);

@@ -777,6 +777,62 @@ KIRAI_EXPORT int kirai_head_linear_gate_bf16(const void* x, const void* w, const
     return head_linear_gate_launch<bf16>(x, w, gate, gate_stride, out, tokens, heads, pad, K, N, stream);
 }
 
+// For many tokens the same product runs on the tensor cores as a grouped product whose groups are the heads: the
+// attention's rows [T, heads, pad] are laid out head by head ([heads, Tpad, pad], Tpad a multiple of 128, zero rows
+// behind a head's last token), every 128-row tile is multiplied with its head's matrix, and the gate kernel brings
+// the 32-bit result [heads, Tpad, N] back token by token, times sigmoid(gate), in bfloat16.
+__global__ void head_major_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int tokens, int padded_tokens, int heads,
+                                  int pad) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int chunks = pad >> 3;  // 16-byte pieces of a row
+    const long total = (long)heads * padded_tokens * chunks;
+    for (long at = (long)blockIdx.x * blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
+        const int c = (int)(at % chunks);
+        const long row = at / chunks;
+        const int t = (int)(row % padded_tokens), h = (int)(row / padded_tokens);
+        uint4 value = make_uint4(0u, 0u, 0u, 0u);
+        if (t < tokens) value = reinterpret_cast<const uint4*>(x + ((size_t)t * heads + h) * pad)[c];
+        reinterpret_cast<uint4*>(out + (size_t)row * pad)[c] = value;
+    }
+}
+
+KIRAI_EXPORT int kirai_head_major_bf16(const void* x, void* out, int tokens, int padded_tokens, int heads, int pad,
+                                       cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || pad <= 0 || padded_tokens < tokens) return KIRAI_ERR_BAD_SIZE;
+    if (pad % 8 != 0 || (((uintptr_t)x | (uintptr_t)out) & 15) != 0) return KIRAI_ERR_BAD_ALIGN;
+    const long total = (long)heads * padded_tokens * (pad / 8);
+    const unsigned blocks = (unsigned)min((total + 255) / 256, (long)148 * 32);
+    return launch_pdl(head_major_kernel, dim3(blocks), dim3(256), 0, stream, 1u, (const bf16*)x, (bf16*)out, tokens, padded_tokens,
+                      heads, pad);
+}
+
+__global__ void head_gate_rows_kernel(const float* __restrict__ y, const float* __restrict__ gate, long gate_stride,
+                                      bf16* __restrict__ out, int tokens, int padded_tokens, int heads, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long total = (long)tokens * heads * n;
+    for (long at = (long)blockIdx.x * blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
+        const int v = (int)(at % n);
+        const long rest = at / n;
+        const int h = (int)(rest % heads), t = (int)(rest / heads);
+        float value = y[((size_t)h * padded_tokens + t) * n + v];
+        if (gate) value *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride + (size_t)h * n + v]));
+        out[at] = __float2bfloat16_rn(value);
+    }
+}
+
+KIRAI_EXPORT int kirai_head_gate_rows_bf16(const float* y, const float* gate, long gate_stride, void* out, int tokens,
+                                           int padded_tokens, int heads, int n, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || n <= 0 || padded_tokens < tokens) return KIRAI_ERR_BAD_SIZE;
+    const long total = (long)tokens * heads * n;
+    const unsigned blocks = (unsigned)min((total + 255) / 256, (long)148 * 32);
+    return launch_pdl(head_gate_rows_kernel, dim3(blocks), dim3(256), 0, stream, 1u, y, gate, gate_stride, (bf16*)out, tokens,
+                      padded_tokens, heads, n);
+}
+
 // ------------------------------------------------------------- element-wise steps
 // x [T, heads, dpad] (in place) *= sigmoid(gate[T, heads * used]) on the first `used` columns of every head; gate is
 // a run of columns of a 32-bit product (row stride gate_stride).
@@ -862,11 +918,50 @@ __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __rest
     }
 }
 
+// The same for bfloat16 rows whose width is a multiple of 8: eight columns a thread, 16-byte loads and stores.
+__global__ void gated_activation_vec_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, long rows, int inter, int act,
+                                            float limit, float slope) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pieces = inter >> 3;
+    const long total = rows * pieces;
+    for (long at = blockIdx.x * (long)blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
+        const long row = at / pieces;
+        const int c = (int)(at - row * pieces);
+        const uint4 g4 = reinterpret_cast<const uint4*>(gate_up + row * 2 * inter)[c];
+        const uint4 u4 = reinterpret_cast<const uint4*>(gate_up + row * 2 * inter + inter)[c];
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+        uint4 packed;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __bfloat1622float2(gp[j]), u = __bfloat1622float2(up[j]);
+            float a, b;
+            if (act == 2) {
+                a = clamped_gated_f32(g.x, u.x, limit, slope);
+                b = clamped_gated_f32(g.y, u.y, limit, slope);
+            } else {
+                a = (act == 1 ? gelu_tanh_f32(g.x) : g.x * sigmoid_f32(g.x)) * u.x;
+                b = (act == 1 ? gelu_tanh_f32(g.y) : g.y * sigmoid_f32(g.y)) * u.y;
+            }
+            op[j] = __floats2bfloat162_rn(a, b);
+        }
+        reinterpret_cast<uint4*>(out + row * inter)[c] = packed;
+    }
+}
+
 template <typename T>
 static int gated_activation_launch(const void* gate_up, void* out, int rows, int inter, int act, float limit, float slope,
                                    cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (inter <= 0 || act < 0 || act > 2 || (act == 2 && !(limit > 0.0f))) return KIRAI_ERR_BAD_SIZE;
+    if (sizeof(T) == 2 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+        const long pieces = (long)rows * (inter / 8);
+        const unsigned vec_blocks = (unsigned)min((pieces + 255) / 256, (long)148 * 16);
+        return launch_pdl(gated_activation_vec_kernel, dim3(vec_blocks), dim3(256), 0, stream, 1u, (const bf16*)gate_up, (bf16*)out,
+                          (long)rows, inter, act, limit, slope);
+    }
     const long total = (long)rows * inter;
     const int threads = 256;
     const unsigned blocks = (unsigned)min((total + threads - 1) / threads, (long)148 * 16);

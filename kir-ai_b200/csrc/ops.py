@@ -352,11 +352,22 @@ def relu2_(x: torch.Tensor) -> torch.Tensor:
     return x
 
 
-def head_linear_gate(x: torch.Tensor, weight: torch.Tensor, heads: int, used: int, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+HEAD_GROUPED_MIN_ROWS = 256  # tokens from which the per-head product runs on the tensor cores as a grouped product
+_head_tiles: dict = {}
+
+
+def head_linear_gate(x: torch.Tensor, weight: torch.Tensor, heads: int, used: int, gate: Optional[torch.Tensor] = None,
+                     padded_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
     """A product per head: ``x`` [T, heads * pad] (the first ``used`` columns of every head count), ``weight``
     [heads, N, used] in the dtype of ``x``; returns [T, heads * N], row t's head h = weight[h] x[t, h], times
-    sigmoid(``gate`` [T, heads * N]) where a gate is given (float32; a run of columns of a wider product is allowed)."""
+    sigmoid(``gate`` [T, heads * N]) where a gate is given (float32; a run of columns of a wider product is allowed).
+    ``padded_weight`` [heads * N, pad] (bfloat16, zero columns beyond ``used``; the columns of ``x`` beyond ``used``
+    must then be finite): with it, steps of many tokens run the product on the tensor cores, the heads as the groups of
+    a grouped product over rows laid out head by head."""
     _need_cuda(x, weight, gate)
+    if (padded_weight is not None and x.dtype == torch.bfloat16 and x.shape[0] >= HEAD_GROUPED_MIN_ROWS and (x.shape[1] // heads) % 8 == 0
+            and x.is_contiguous() and x.data_ptr() % 16 == 0):
+        return _head_linear_gate_grouped(x, padded_weight, heads, weight.shape[1], gate)
     assert x.dim() == 2 and x.is_contiguous() and x.shape[1] % heads == 0
     pad = x.shape[1] // heads
     assert weight.dim() == 3 and weight.is_contiguous() and weight.dtype == x.dtype and weight.shape[0] == heads and weight.shape[2] == used <= pad
@@ -367,6 +378,28 @@ def head_linear_gate(x: torch.Tensor, weight: torch.Tensor, heads: int, used: in
     _call(f"kirai_head_linear_gate_{_suffix(x.dtype)}", _ptr(x), _ptr(weight), _ptr(gate), _l(gate.stride(0) if gate is not None else 0),
           _ptr(out), _i(x.shape[0]), _i(heads), _i(pad), _i(used), _i(n), _stream(),
           detail=f" t={x.shape[0]} heads={heads} k={used} n={n}" if _timer is not None else "")
+    return out
+
+
+def _head_linear_gate_grouped(x: torch.Tensor, padded_weight: torch.Tensor, heads: int, n: int, gate: Optional[torch.Tensor]) -> torch.Tensor:
+    tokens, pad = x.shape[0], x.shape[1] // heads
+    padded = -(-tokens // 128) * 128
+    assert padded_weight.dtype == torch.bfloat16 and padded_weight.shape == (heads * n, pad) and padded_weight.is_contiguous()
+    key = (x.device, heads, padded)
+    tile_group = _head_tiles.get(key)
+    if tile_group is None:  # tile i of the head-major rows belongs to head i // (padded / 128)
+        if len(_head_tiles) > 64:
+            _head_tiles.clear()
+        tile_group = (torch.arange(heads * (padded // 128), dtype=torch.int32) // (padded // 128)).to(torch.int32).to(x.device)
+        _head_tiles[key] = tile_group
+    rows = torch.empty((heads * padded, pad), dtype=torch.bfloat16, device=x.device)
+    _call("kirai_head_major_bf16", _ptr(x), _ptr(rows), _i(tokens), _i(padded), _i(heads), _i(pad), _stream())
+    y = linear_grouped(rows, padded_weight, heads, tile_group, out_dtype=torch.float32)
+    out = torch.empty((tokens, heads * n), dtype=torch.bfloat16, device=x.device)
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape == (tokens, heads * n)
+    _call("kirai_head_gate_rows_bf16", _ptr(y), _ptr(gate), _l(gate.stride(0) if gate is not None else 0), _ptr(out), _i(tokens),
+          _i(padded), _i(heads), _i(n), _stream())
     return out
 
 

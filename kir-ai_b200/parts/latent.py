@@ -66,6 +66,7 @@ class LatentAttention(Mixer):
         else:
             self.out = Linear([("", hidden_size)], heads * self.pad_dim)     # filled from o and uv at load
         self.up_v: Optional[torch.Tensor] = None                             # [heads, value_dim, kv_rank], with a gate
+        self.up_v_padded: Optional[torch.Tensor] = None                      # [heads * value_dim, pad_dim], zero columns
         self.q_norm = self.kv_norm = None
 
     def cache_need(self) -> KVCacheNeed:
@@ -103,6 +104,11 @@ class LatentAttention(Mixer):
         if self.gate_name:
             # the gate stands between W_uv and W_o: both stay as stored
             self.up_v = weights.stored(n["uv"]).to(device=rt.device, dtype=rt.dtype).view(H, dv, kr).contiguous()
+            self.up_v_padded = None
+            if rt.dtype == torch.bfloat16 and self.pad_dim % 8 == 0:
+                # for steps of many tokens: the heads' matrices as the groups of one grouped product over padded rows
+                self.up_v_padded = torch.zeros((H * dv, self.pad_dim), dtype=rt.dtype, device=rt.device)
+                self.up_v_padded[:, :kr] = self.up_v.view(H * dv, kr)
             self.out.load(weights, rt)
             return
         # the output projection reads the heads' sums of latents: columns W_o,i W_uv,i, zero where a row is padding
@@ -126,5 +132,6 @@ class LatentAttention(Mixer):
         mixed = ops.paged_attention(q, cache.kv, table, batch, None, self.scale)
         if self.gate_name:
             gate = down[:, self.q_rank + self.kv_rank + self.rot_dim :]
-            mixed = ops.head_linear_gate(mixed.view(mixed.shape[0], -1), self.up_v, self.heads, self.kv_rank, gate)
+            mixed = ops.head_linear_gate(mixed.view(mixed.shape[0], -1), self.up_v, self.heads, self.kv_rank, gate,
+                                         padded_weight=self.up_v_padded)
         return self.out.forward(mixed, self.out_dtype)

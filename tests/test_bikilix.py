@@ -393,8 +393,11 @@ def test_router_leaves_closed_groups_closed_also_below_zero(dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,used,pad,n,tokens", [(4, 16, 24, 16, 7), (3, 18, 24, 12, 40), (2, 600, 608, 40, 19), (16, 96, 128, 32, 300), (1, 5, 8, 3, 1)])
+@pytest.mark.parametrize("heads,used,pad,n,tokens", [(4, 16, 24, 16, 7), (3, 18, 24, 12, 40), (2, 600, 608, 40, 19), (16, 96, 128, 32, 300), (1, 5, 8, 3, 1),
+                                                     (16, 192, 256, 64, 700), (3, 18, 24, 12, 257)])
 def test_a_product_per_head_with_its_gate(dtype, heads, used, pad, n, tokens):
+    """On the CUDA cores, and (bfloat16, many tokens, given the matrices with zero columns up to the padded width) as a
+    grouped product on the tensor cores with the heads as groups; columns beyond a head's used ones do not count."""
     from kirai_b200.csrc import ops
 
     g = torch.Generator().manual_seed(heads * n)
@@ -407,6 +410,15 @@ def test_a_product_per_head_with_its_gate(dtype, heads, used, pad, n, tokens):
     gate = wide.cuda()[:, 5:]  # a run of columns of a wider product
     got = ops.head_linear_gate(x.reshape(tokens, heads * pad).cuda(), w.cuda(), heads, used, gate)
     close(dtype, got.float().cpu(), expected * torch.sigmoid(wide[:, 5:].double()), "with its gate")
+    if dtype == torch.bfloat16:
+        padded = torch.zeros((heads * n, pad), dtype=dtype)
+        padded[:, :used] = w.reshape(heads * n, used)
+        for g in (None, gate):
+            got = ops.head_linear_gate(x.reshape(tokens, heads * pad).cuda(), w.cuda(), heads, used, g, padded_weight=padded.cuda())
+            factor = 1.0 if g is None else torch.sigmoid(wide[:, 5:].double())
+            close(dtype, got.float().cpu(), expected * factor, "given the padded matrices")
+        if tokens >= ops.HEAD_GROUPED_MIN_ROWS and pad % 8 == 0:
+            assert ops.launch_counts.get("kirai_head_major_bf16", 0) > 0
 
 
 def _mixer_part(entry, width):
