@@ -363,7 +363,14 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
         flops = bytes_ = simt = 0.0
         label = name
         match = re.search(r"m=(\d+) n=(\d+) k=(\d+) form=(\d+)", name)
-        if match and "grouped" in name:
+        if match and "grouped" in name and design == "bikilix" and int(match.group(2)) == BIKILIX_LATENT["vdim"] \
+                and int(match.group(3)) == BIKILIX_LATENT["kv_rank"] + BIKILIX_LATENT["rot_dim"]:
+            # the heads' value matrices as groups over rows laid out head by head: the design's work is kv_rank columns a head
+            h_, k_, n_ = BIKILIX_LATENT["heads"], BIKILIX_LATENT["kv_rank"], BIKILIX_LATENT["vdim"]
+            flops = 2.0 * tokens * h_ * k_ * n_ * count
+            bytes_ = (tokens * h_ * (2.0 * k_ + 4.0 * n_) + 2.0 * h_ * k_ * n_) * count
+            label += " (a product per head, heads as groups)"
+        elif match and "grouped" in name:
             # rows sorted by expert: the design's work is tokens * top rows through one expert's matrices each
             m, n, k, form = map(int, match.groups())
             rows_used = tokens * size["top"]
@@ -397,6 +404,8 @@ def _kernel_rows(summary: dict, tokens: int, context_pairs: float, cache_rows: f
             t_, h_, k_, n_ = (int(v) for v in re.search(r"t=(\d+) heads=(\d+) k=(\d+) n=(\d+)", name).groups())
             flops = 2.0 * t_ * h_ * k_ * n_ * count
             bytes_ = (2.0 * t_ * h_ * (k_ + n_) + 4.0 * t_ * h_ * n_ + 2.0 * h_ * k_ * n_) * count
+        elif "add_bias" in name:
+            bytes_ = tokens * width * 8.0 * count
         elif "norm_add_norm" in name:
             bytes_ = tokens * width * 14.0 * count
         elif "stream_copy" in name:

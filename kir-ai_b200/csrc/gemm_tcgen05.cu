@@ -111,8 +111,10 @@ struct Epilogue {
     // of A's tile m are multiplied with matrix tile_group[m] (rows of A sorted by group, every group's rows padded to
     // whole tiles); a tile with a negative group holds no rows and is left out.  Null: one matrix.
     const int* tile_group = nullptr;
-    // The activation of the gated epilogue (EPI 1): 0 silu, 1 the tanh form of gelu.
+    // The activation of the gated epilogue (EPI 1): 0 silu, 1 the tanh form of gelu, 2 the clamped form: with
+    // g = min(gate, gate_limit) and u = clamp(up, -gate_limit, gate_limit) the result is g sigmoid(gate_slope g) (u + 1).
     int gate_act = 0;
+    float gate_limit = 0.0f, gate_slope = 1.0f;
 };
 
 // Clock stamps of one CTA of the streaming kernel, written only when a buffer is given: 0 the CTA starts, 1 the kernel
@@ -180,8 +182,13 @@ __device__ __forceinline__ float silu_mul(float gate, float up) {
 }
 // act(gate) * up.  The tanh form of gelu, 0.5 z (1 + tanh(y)) with y = sqrt(2 / pi) (z + 0.044715 z^3), is
 // z * sigmoid(2 y): the same one exponential and one division as silu, with another argument.
-__device__ __forceinline__ float gate_mul(int act, float gate, float up) {
-    const float t = act == 1 ? 1.5957691216057308f * fmaf(0.044715f * gate * gate, gate, gate) : gate;
+__device__ __forceinline__ float gate_mul(const Epilogue& ep, float gate, float up) {
+    if (ep.gate_act == 2) {
+        const float g = fminf(gate, ep.gate_limit);
+        const float u = fminf(fmaxf(up, -ep.gate_limit), ep.gate_limit);
+        return __fdividef(g * (u + 1.0f), 1.0f + __expf(-ep.gate_slope * g));
+    }
+    const float t = ep.gate_act == 1 ? 1.5957691216057308f * fmaf(0.044715f * gate * gate, gate, gate) : gate;
     return __fdividef(gate * up, 1.0f + __expf(-t));
 }
 
@@ -478,7 +485,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float out = gate_mul(ep.gate_act, v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
+                        const float out = gate_mul(ep, v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
                         if ((lane & 8) == 0) stage[(c0 - h0 + j) * 132 + (tile_row >> 4) * 8 + (tile_row & 7)] = out;
                     }
                 } else {
@@ -510,7 +517,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 // this lane holds weight row x_row: rows 16k..16k+7 are gate rows, 16k+8..16k+15 their up rows
                 float out[16];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) out[j] = gate_mul(ep.gate_act, v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
+                for (int j = 0; j < 16; ++j) out[j] = gate_mul(ep, v[j], __shfl_xor_sync(0xffffffffu, v[j], 8));
                 if ((lane & 8) == 0 && x_row < x_rows) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -528,14 +535,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     uint32_t packed[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        __nv_bfloat162 pair = __floats2bfloat162_rn(gate_mul(ep.gate_act, v[2 * j], v[2 * j + 8]), gate_mul(ep.gate_act, v[2 * j + 1], v[2 * j + 9]));
+                        __nv_bfloat162 pair = __floats2bfloat162_rn(gate_mul(ep, v[2 * j], v[2 * j + 8]), gate_mul(ep, v[2 * j + 1], v[2 * j + 9]));
                         packed[j] = *reinterpret_cast<uint32_t*>(&pair);
                     }
                     *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        if (y0 + c0 + j + 8 < y_rows) dst[j] = from_f32<OutT>(gate_mul(ep.gate_act, v[j], v[j + 8]));
+                        if (y0 + c0 + j + 8 < y_rows) dst[j] = from_f32<OutT>(gate_mul(ep, v[j], v[j + 8]));
                 }
             } else if (SWAP) {
 #pragma unroll
@@ -997,14 +1004,14 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                         uint32_t packed[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            __nv_bfloat162 pair = __floats2bfloat162_rn(gate_mul(ep.gate_act, v[2 * j], v[2 * j + 8]), gate_mul(ep.gate_act, v[2 * j + 1], v[2 * j + 9]));
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(gate_mul(ep, v[2 * j], v[2 * j + 8]), gate_mul(ep, v[2 * j + 1], v[2 * j + 9]));
                             packed[j] = *reinterpret_cast<uint32_t*>(&pair);
                         }
                         *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     } else {
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            if (y0 + c0 + j + 8 < N) dst[j] = from_f32<OutT>(gate_mul(ep.gate_act, v[j], v[j + 8]));
+                            if (y0 + c0 + j + 8 < N) dst[j] = from_f32<OutT>(gate_mul(ep, v[j], v[j + 8]));
                     }
                 } else {
                     OutT* dst = C + (size_t)x_row * ldc + y0 + c0;
@@ -1246,9 +1253,11 @@ KIRAI_EXPORT void kirai_gemm_bf16_set_stamps(unsigned long long* buffer) { g_gem
 // A grouped product for rows sorted by group: A [M, K] (M a multiple of 128), W = `groups` matrices [N, K] one after the
 // other (row-major [groups * N, K]; or tiled, every matrix a whole number of 128-row boxes: N a multiple of 128),
 // tile_group [M / 128] (on the device) = the matrix of each 128-row tile of A.  C [M, N].
-//   form 0: bf16.  1: float.  4: bf16 relu(product)^2.
+//   form 0: bf16.  1: float.  4: bf16 relu(product)^2.  6: C [M, N / 2] bf16 = act(gate) * up, every matrix's rows in
+//   groups of 8 gate rows followed by their 8 up rows, act as Epilogue::gate_act with gate_limit and gate_slope.
 KIRAI_EXPORT int kirai_gemm_bf16_grouped(const void* A, const void* W, int tiled, void* C, int M, int N, int K, long lda, long ldc,
-                                         int groups, const int* tile_group, int form, int* error_flag, cudaStream_t stream) {
+                                         int groups, const int* tile_group, int form, int gate_act, float gate_limit,
+                                         float gate_slope, int* error_flag, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || groups <= 0 || !tile_group || M % GEMM_BM != 0) return KIRAI_ERR_BAD_SIZE;
     if (K % 8 != 0 || lda % 8 != 0) return KIRAI_ERR_BAD_ALIGN;
@@ -1262,6 +1271,10 @@ KIRAI_EXPORT int kirai_gemm_bf16_grouped(const void* A, const void* W, int tiled
         case 0: KIRAI_GROUPED(bf16, 0);
         case 1: KIRAI_GROUPED(float, 0);
         case 4: KIRAI_GROUPED(bf16, 3);
+        case 6:
+            if (N % 16 != 0 || gate_act < 0 || gate_act > 2 || (gate_act == 2 && !(gate_limit > 0.0f))) return KIRAI_ERR_BAD_SIZE;
+            ep.gate_act = gate_act, ep.gate_limit = gate_limit, ep.gate_slope = gate_slope;
+            KIRAI_GROUPED(bf16, 1);
     }
 #undef KIRAI_GROUPED
     return KIRAI_ERR_BAD_SIZE;

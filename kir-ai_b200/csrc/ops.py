@@ -798,17 +798,18 @@ def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
 
 
 def gated_expert_gate(gate_up: torch.Tensor, gates: torch.Tensor, ff: int, activation: str = "silu", limit: float = 0.0,
-                      slope: float = 1.0) -> torch.Tensor:
+                      slope: float = 1.0, interleaved: bool = False) -> torch.Tensor:
     """Stacked gated experts: ``gate_up`` [T, experts * 2 ff] (per expert ff gate columns, then ff up columns) becomes
     [T, experts * ff] = act(gate) * up * gates[t, expert] (``gates`` float32 [T, experts], zero where not chosen);
-    the activations are those of ``gated_activation``."""
+    the activations are those of ``gated_activation``.  ``interleaved``: an expert's columns come as 8 gate columns,
+    their 8 up columns, 8 gate columns, ... (see ``interleave_gate_up``)."""
     _need_cuda(gate_up, gates)
     assert gate_up.dim() == 2 and gate_up.is_contiguous() and gates.dtype == torch.float32 and gates.is_contiguous()
     experts = gates.shape[1]
     assert gate_up.shape == (gates.shape[0], experts * 2 * ff)
     out = torch.empty((gate_up.shape[0], experts * ff), dtype=gate_up.dtype, device=gate_up.device)
     _call(f"kirai_gated_expert_gate_{_suffix(gate_up.dtype)}", _ptr(gate_up), _ptr(gates), _ptr(out), _i(gate_up.shape[0]),
-          _i(experts), _i(ff), _i(GATED_ACTIVATIONS[activation]), _f(limit), _f(slope), _stream())
+          _i(experts), _i(ff), _i(GATED_ACTIVATIONS[activation]), _f(limit), _f(slope), _i(int(interleaved)), _stream())
     return out
 
 
@@ -954,20 +955,26 @@ def route_combine_norm_add(resid: torch.Tensor, y: torch.Tensor, slot_of: torch.
 
 
 def linear_grouped(x: torch.Tensor, weight, groups: int, tile_group: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-                   relu2: bool = False) -> torch.Tensor:
+                   relu2: bool = False, gated: Optional[tuple] = None) -> torch.Tensor:
     """Rows sorted by group times one of ``groups`` stacked matrices each: ``x`` [tiles * 128, K] (bfloat16), ``weight``
     [groups * N, K] (row-major, or a ``TiledWeight`` with N a multiple of 128), ``tile_group`` [tiles] the matrix of each
-    128-row tile.  Returns [tiles * 128, N]; with ``relu2`` relu(product)^2 (bfloat16)."""
+    128-row tile.  Returns [tiles * 128, N]; with ``relu2`` relu(product)^2 (bfloat16).  ``gated`` = (activation, limit,
+    slope): every matrix holds 8 gate rows, their 8 up rows, 8 gate rows, ... and the result is act(gate) * up,
+    [tiles * 128, N / 2] (bfloat16), the activations those of ``gated_activation``."""
     m, k, total = _check_product(x, weight)
     _need_cuda(tile_group)
     assert total % groups == 0 and m % 128 == 0 and tile_group.dtype == torch.int32 and tile_group.numel() == m // 128
     n = total // groups
     tiled = isinstance(weight, TiledWeight)
-    assert not relu2 or out_dtype == torch.bfloat16
-    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    form = 4 if relu2 else (0 if out_dtype == torch.bfloat16 else 1)
+    assert not (relu2 or gated) or out_dtype == torch.bfloat16
+    assert not (relu2 and gated) and (gated is None or n % 16 == 0)
+    width = n // 2 if gated else n
+    out = torch.empty((m, width), dtype=out_dtype, device=x.device)
+    form = 6 if gated else (4 if relu2 else (0 if out_dtype == torch.bfloat16 else 1))
+    act, limit, slope = (GATED_ACTIVATIONS[gated[0]], float(gated[1]), float(gated[2])) if gated else (0, 0.0, 1.0)
     _call("kirai_gemm_bf16_grouped", _ptr(x), _ptr(weight.boxes if tiled else weight), _i(tiled), _ptr(out), _i(m), _i(n), _i(k),
-          _l(x.stride(0)), _l(n), _i(groups), _ptr(tile_group), _i(form), _ptr(error_flag(x.device)), _stream(),
+          _l(x.stride(0)), _l(width), _i(groups), _ptr(tile_group), _i(form), _i(act), _f(limit), _f(slope),
+          _ptr(error_flag(x.device)), _stream(),
           detail=f" m={m} n={n} k={k} form={form}" if _timer is not None else "")
     return out
 

@@ -524,9 +524,11 @@ KIRAI_EXPORT int kirai_softcap_rows(float* x, float cap, long total, cudaStream_
 // Stacked gated experts: gate_up [T, experts * 2 ff], per expert ff gate columns and then ff up columns;
 // out [T, experts * ff] = act(gate) * up * gates[t, expert] (gates float32 [T, experts], zero where not chosen).
 // act 0: silu, 1: the tanh form of gelu, 2: the clamped form (clamped_gated_f32 with `limit` and `slope`).
+// `interleaved`: an expert's columns come as 8 gate columns, their 8 up columns, 8 gate columns, ... (the order in which
+// the tensor-core product's gated epilogue wants the matrices' rows; ff a multiple of 8).
 template <typename T>
 __global__ void gated_expert_gate_kernel(const T* __restrict__ gate_up, const float* __restrict__ gates, T* __restrict__ out,
-                                         long rows, int experts, int ff, int act, float limit, float slope) {
+                                         long rows, int experts, int ff, int act, float limit, float slope, int interleaved) {
     pdl_launch_dependents();
     pdl_wait();
     const long per_row = (long)experts * ff, total = rows * per_row;
@@ -538,7 +540,8 @@ __global__ void gated_expert_gate_kernel(const T* __restrict__ gate_up, const fl
         float value = 0.0f;
         if (weight != 0.0f) {
             const T* src = gate_up + row * 2 * per_row + (long)e * 2 * ff;
-            const float g = to_f32<T>(src[j]), u = to_f32<T>(src[ff + j]);
+            const int at_gate = interleaved ? ((j >> 3) << 4) + (j & 7) : j;
+            const float g = to_f32<T>(src[at_gate]), u = to_f32<T>(src[interleaved ? at_gate + 8 : ff + j]);
             value = act == 2 ? clamped_gated_f32(g, u, limit, slope) * weight : (act == 1 ? sf_gelu_tanh(g) : sf_silu(g)) * u * weight;
         }
         out[at] = from_f32<T>(value);
@@ -547,20 +550,21 @@ __global__ void gated_expert_gate_kernel(const T* __restrict__ gate_up, const fl
 
 template <typename T>
 static int gated_expert_gate_launch(const void* gate_up, const float* gates, void* out, int rows, int experts, int ff, int act,
-                                    float limit, float slope, cudaStream_t stream) {
+                                    float limit, float slope, int interleaved, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (experts <= 0 || ff <= 0 || act < 0 || act > 2 || (act == 2 && !(limit > 0.0f))) return KIRAI_ERR_BAD_SIZE;
+    if (experts <= 0 || ff <= 0 || act < 0 || act > 2 || (act == 2 && !(limit > 0.0f)) || (interleaved && ff % 8 != 0))
+        return KIRAI_ERR_BAD_SIZE;
     const long total = (long)rows * experts * ff;
     const unsigned blocks = (unsigned)min((total + 255) / 256, (long)148 * 16);
     return launch_pdl(gated_expert_gate_kernel<T>, dim3(blocks), dim3(256), 0, stream, 1u, (const T*)gate_up, gates, (T*)out,
-                      (long)rows, experts, ff, act, limit, slope);
+                      (long)rows, experts, ff, act, limit, slope, interleaved);
 }
 
 KIRAI_EXPORT int kirai_gated_expert_gate_f32(const void* gate_up, const float* gates, void* out, int rows, int experts, int ff,
-                                             int act, float limit, float slope, cudaStream_t stream) {
-    return gated_expert_gate_launch<float>(gate_up, gates, out, rows, experts, ff, act, limit, slope, stream);
+                                             int act, float limit, float slope, int interleaved, cudaStream_t stream) {
+    return gated_expert_gate_launch<float>(gate_up, gates, out, rows, experts, ff, act, limit, slope, interleaved, stream);
 }
 KIRAI_EXPORT int kirai_gated_expert_gate_bf16(const void* gate_up, const float* gates, void* out, int rows, int experts, int ff,
-                                              int act, float limit, float slope, cudaStream_t stream) {
-    return gated_expert_gate_launch<bf16>(gate_up, gates, out, rows, experts, ff, act, limit, slope, stream);
+                                              int act, float limit, float slope, int interleaved, cudaStream_t stream) {
+    return gated_expert_gate_launch<bf16>(gate_up, gates, out, rows, experts, ff, act, limit, slope, interleaved, stream);
 }

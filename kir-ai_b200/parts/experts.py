@@ -28,9 +28,10 @@ This path keeps a second copy of the down matrices, stacked along the output
 axis.  Neither path waits for the host.
 
 Options.  ``activation="silu_gated"``: an expert is down(silu(gate x) * (up x)) with a gate matrix of its own; the
-experts' gate and up matrices are stacked expert by expert ([gate_e; up_e]), the few-token kernel applies the gated
-activation and the routing weight together, and the many-token path runs the grouped product without an epilogue and
-the framework's gated-activation kernel on its rows.  ``scoring="softmax_all"``: the weights are the chosen experts'
+experts' gate and up matrices are stacked expert by expert ([gate_e; up_e]; where the expert size is a multiple of 8, with
+the rows of each in turns of eight, the order of the tensor-core product's gated epilogue), the few-token kernel applies
+the gated activation and the routing weight together, and the many-token path runs the grouped product with the
+activation in its epilogue (other expert sizes: without an epilogue, then the framework's gated-activation kernel).  ``scoring="softmax_all"``: the weights are the chosen experts'
 shares of the softmax over ALL experts' logits, not renormalised (the choice is the same: the largest logits).
 ``shared``: a feed-forward that runs for every token beside the routed experts; its output is added (``forward_terms``
 hands both terms to whoever adds them into the stream).
@@ -95,10 +96,17 @@ class RoutedExperts(FeedForward):
         self.activation = activation
         self.out_dtype = out_dtype
         self.router_name = prefix + n["router"]
+        self.interleaved = self.gated and expert_size % 8 == 0
         if self.gated:
-            # expert by expert: its gate rows, then its up rows
+            # expert by expert: its gate rows, then its up rows; where the expert size allows, in the order of the
+            # tensor-core product's gated epilogue instead: 8 gate rows, their 8 up rows, 8 gate rows, ...
+            order = None
+            if self.interleaved:
+                block = torch.arange(expert_size).view(expert_size // 8, 1, 8)
+                one = torch.cat([block, block + expert_size], dim=1).reshape(-1)  # of one expert's 2 * expert_size rows
+                order = (torch.arange(experts)[:, None] * (2 * expert_size) + one[None, :]).reshape(-1)
             self.up = Linear([(prefix + n[kind].format(e=e), expert_size) for e in range(experts) for kind in ("gate", "up")],
-                             hidden_size)
+                             hidden_size, row_order=order)
         else:
             self.up = Linear([(prefix + n["up"].format(e=e), expert_size) for e in range(experts)], hidden_size)
         self.down = Linear([(prefix + n["down"].format(e=e), expert_size) for e in range(experts)], hidden_size,
@@ -162,7 +170,9 @@ class RoutedExperts(FeedForward):
         _, ids, mix = self._route(x, True)
         tile_group, slot_of, row_of_slot = ops.route_plan(ids, self.experts)
         rows = ops.route_gather(x, row_of_slot)
-        if self.gated:
+        if self.gated and self.interleaved:
+            hidden = ops.linear_grouped(rows, self.up.weight, self.experts, tile_group, gated=(self.gate_act, self.limit, self.slope))
+        elif self.gated:
             hidden = ops.gated_activation(ops.linear_grouped(rows, self.up.weight, self.experts, tile_group), self.gate_act,
                                           self.limit, self.slope)
         else:
@@ -201,7 +211,8 @@ class RoutedExperts(FeedForward):
         gates = self._route(x, False)
         hidden = self.up.forward(x)
         if self.gated:
-            hidden = ops.gated_expert_gate(hidden, gates, self.expert_size, self.gate_act, self.limit, self.slope)
+            hidden = ops.gated_expert_gate(hidden, gates, self.expert_size, self.gate_act, self.limit, self.slope,
+                                           interleaved=self.interleaved)
         else:
             ops.relu2_gate_(hidden, gates, self.expert_size)
         return self.down.forward(hidden, self.out_dtype)
