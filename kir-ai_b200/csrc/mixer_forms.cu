@@ -823,10 +823,41 @@ __global__ void head_gate_rows_kernel(const float* __restrict__ y, const float* 
     }
 }
 
+// The same, four columns a thread (n and the gate's row stride multiples of 4, 16-byte aligned buffers).
+__global__ void head_gate_rows_vec_kernel(const float* __restrict__ y, const float* __restrict__ gate, long gate_stride,
+                                          bf16* __restrict__ out, int tokens, int padded_tokens, int heads, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int quads = n >> 2;
+    const long total = (long)tokens * heads * quads;
+    for (long at = (long)blockIdx.x * blockDim.x + threadIdx.x; at < total; at += (long)gridDim.x * blockDim.x) {
+        const int q = (int)(at % quads);
+        const long rest = at / quads;
+        const int h = (int)(rest % heads), t = (int)(rest / heads);
+        float4 value = reinterpret_cast<const float4*>(y + ((size_t)h * padded_tokens + t) * n)[q];
+        if (gate) {
+            const float4 g = reinterpret_cast<const float4*>(gate + (size_t)t * gate_stride + (size_t)h * n)[q];
+            value.x *= 1.0f / (1.0f + expf(-g.x)), value.y *= 1.0f / (1.0f + expf(-g.y));
+            value.z *= 1.0f / (1.0f + expf(-g.z)), value.w *= 1.0f / (1.0f + expf(-g.w));
+        }
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(value.x, value.y), hi = __floats2bfloat162_rn(value.z, value.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(out)[at] = packed;
+    }
+}
+
 KIRAI_EXPORT int kirai_head_gate_rows_bf16(const float* y, const float* gate, long gate_stride, void* out, int tokens,
                                            int padded_tokens, int heads, int n, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (heads <= 0 || n <= 0 || padded_tokens < tokens) return KIRAI_ERR_BAD_SIZE;
+    if (n % 4 == 0 && gate_stride % 4 == 0 && (((uintptr_t)y | (uintptr_t)gate | (uintptr_t)out) & 15) == 0) {
+        const long pieces = (long)tokens * heads * (n / 4);
+        const unsigned vec_blocks = (unsigned)min((pieces + 255) / 256, (long)148 * 32);
+        return launch_pdl(head_gate_rows_vec_kernel, dim3(vec_blocks), dim3(256), 0, stream, 1u, y, gate, gate_stride, (bf16*)out,
+                          tokens, padded_tokens, heads, n);
+    }
     const long total = (long)tokens * heads * n;
     const unsigned blocks = (unsigned)min((total + 255) / 256, (long)148 * 32);
     return launch_pdl(head_gate_rows_kernel, dim3(blocks), dim3(256), 0, stream, 1u, y, gate, gate_stride, (bf16*)out, tokens,
