@@ -3,7 +3,10 @@
 //   * embedding rows times a constant, plus a sinusoidal position vector (column 2i the sine and column 2i + 1
 //     the cosine of position * frequency[i], angles in 32-bit);
 //   * the norm on a sub-layer's OUTPUT: stream += y / sqrt(mean(y^2) + eps) * w, with the runtime-dtype copy of the
-//     new stream that the next sub-layer reads written in the same pass;
+//     new stream that the next sub-layer reads written in the same pass; the same followed by the norm that reads the
+//     stream next (norm_add_norm), and with the stream's copy written into a run of columns of a wider buffer
+//     (stream_copy: two streams side by side for one product);
+//   * relu(z)^2 in place;
 //   * the preparation of attention whose q, k, v projections carry biases and whose queries and keys are normed
 //     over the WHOLE projection (all heads of a token at once, one weight per column), with keys and values of
 //     their own widths: bias, norm, queries out (heads padded to the cache's head width), keys and values to their

@@ -178,7 +178,7 @@ def test_frequencies_stretched_by_index_and_the_order_of_neighbours():
     import kirai_b200  # noqa: F401
     from kirai_b200.parts import RotaryEmbedding
 
-    for dims, base, scaling in ((8, 300.0, (4.0, 32, 8.0, 1.0)), (6, 50.0, (2.0, 16, 4.0, 0.5)), (32, 500000.0, (8.0, 512, 32.0, 1.0)),
+    for dims, base, scaling in ((8, 300.0, (4.0, 32, 8.0, 1.0)), (6, 50.0, (2.0, 16, 4.0, 0.5)), (32, 250000.0, (6.0, 1024, 16.0, 2.0)),
                                 (16, 10000.0, None)):
         table, amplitude = plain.pair_frequencies(rot(base, dims, scaling))
         part = RotaryEmbedding(dims, base, dims, scaling=dict(zip(("factor", "original", "fast", "slow"), scaling)) if scaling else None,
@@ -336,7 +336,7 @@ EXPERT_CASES = [
     (moe(16, 0.4, 8, 2, 4, 2), 64, 40),
     (moe(12, 0.25, 5, 2, 1, 1), 100, 40),      # one group: no limit on the choice
     (moe(20, 2.0, 6, 1, 2, 2), 36, 40),        # every group open, one expert a token
-    (moe(8, 1.5, 12, 3, 3, 2), 48, 1300),      # the many-token router kernel
+    (moe(8, 1.3, 15, 3, 5, 2), 48, 1300),      # the many-token router kernel
     (moe(8, 0.7, 6, 4, 6, 5), 24, 9),          # groups of one expert
     (moe(128, 1.0, 8, 2, 4, 2), 128, 700),     # rows sorted by expert on the tensor cores (bfloat16)
     (moe(16, 0.6, 40, 4, 5, 3), 64, 200),      # more experts than a warp has lanes
@@ -456,7 +456,7 @@ PART_CASES = [
     (attn(2, 2, 32, 32, 2.0, rot(10000.0, 32), 33), 64, 4),
     (attn(3, 3, 10, 10, 2.5, rot(50.0, 10), 1), 24, 2),           # a window of one: every token sees itself alone
     (attn(8, 2, 64, 64, 0.8, rot(10000.0, 48), 48), 128, 16),
-    (attn(4, 2, 128, 128, 0.5, rot(1e6, 32), 200), 96, 16),       # a window wider than the sequence
+    (attn(6, 2, 128, 128, 0.5, rot(2e5, 64), 200), 96, 16),       # a window wider than the sequence
     (attn(4, 2, 256, 136, 0.4, rot(10000.0, 64), 40), 128, 16),
     (attn(2, 1, 24, 24, 1.0, rot(100.0, 8), None), 40, 4),        # no mask: every earlier token
     (latent(4, 8, 8, 16, 24, 16, 1.5, base=300.0, scaling=(4.0, 32, 8.0, 1.0)), 64, 4),
